@@ -97,6 +97,12 @@ class ModelSpec:
     logit_softcap: Optional[float] = None     # logits become cap * tanh(logits / cap) (None: not)
     # tensors that belong to no layer: local name -> (tensor name in the checkpoint, shape); held in float32
     extra_tensors: Mapping[str, Tuple[str, Tuple[int, ...]]] = field(default_factory=dict)
+    # a part of category ``entry`` that adds to the token rows as they enter the stream, with "<param>" -> tensor name
+    entry: Optional[PartSpec] = None
+    entry_names: Mapping[str, str] = field(default_factory=dict)
+    # the residual stream is kept in this many copies, all equal to the entering rows at the start; the layers'
+    # blocks and the final norm must be kinds that read and write such a stream (None: the plain stream [N, hidden])
+    stream_copies: Optional[int] = None
 
     def __post_init__(self):
         for i, e in enumerate(self.schedule):

@@ -23,8 +23,8 @@ constexpr int kMaxTop = 32;
 
 // The choice of one token by one warp: softmax over `logit(e)`, the `top` largest, renormalised.
 template <typename F>
-__device__ __forceinline__ void choose_experts(F logit, int E, int top, float eps, int lane, int32_t* __restrict__ ids,
-                                               float* __restrict__ weights) {
+__device__ __forceinline__ void choose_experts(F logit, int E, int top, float eps, float factor, int lane,
+                                               int32_t* __restrict__ ids, float* __restrict__ weights) {
   constexpr int kPer = kMaxExperts / 32;
   float s[kPer];
   float m = -INFINITY;
@@ -78,12 +78,13 @@ __device__ __forceinline__ void choose_experts(F logit, int E, int top, float ep
   }
   if (lane < top) {
     ids[lane] = chosen_e;
-    weights[lane] = chosen_w / (total + eps);
+    // eps < 0: the chosen scores stand as they are (no division by their sum); `factor` multiplies either form
+    weights[lane] = (eps < 0.f ? chosen_w : chosen_w / (total + eps)) * factor;
   }
 }
 
 // From given logits: one warp per token.
-__global__ void route_topk_kernel(const float* __restrict__ logits, int E, int top, float eps,
+__global__ void route_topk_kernel(const float* __restrict__ logits, int E, int top, float eps, float factor,
                                   const int32_t* __restrict__ req_of_token, int32_t* __restrict__ ids,
                                   float* __restrict__ weights, int n_tokens) {
   pdl_launch_dependents();
@@ -98,7 +99,7 @@ __global__ void route_topk_kernel(const float* __restrict__ logits, int E, int t
     return;
   }
   const float* z = logits + (size_t)n * E;
-  choose_experts([&](int e) { return z[e]; }, E, top, eps, lane, ids + (size_t)n * top, weights + (size_t)n * top);
+  choose_experts([&](int e) { return z[e]; }, E, top, eps, factor, lane, ids + (size_t)n * top, weights + (size_t)n * top);
 }
 
 // Four consecutive values of a row kept in shared memory (the address a multiple of four elements).
@@ -119,7 +120,7 @@ __device__ __forceinline__ void load4(const __nv_bfloat16* p, float& a, float& b
 // TOK is); then warp t chooses for token t.
 template <typename T, int TOK>
 __global__ void route_kernel(const T* __restrict__ x, long x_stride, const float* __restrict__ w, int E, int K, int top,
-                             float eps, const int32_t* __restrict__ req_of_token, int32_t* __restrict__ ids,
+                             float eps, float factor, const int32_t* __restrict__ req_of_token, int32_t* __restrict__ ids,
                              float* __restrict__ weights, int n_tokens) {
   extern __shared__ __align__(16) unsigned char route_smem[];   // [TOK][K] rows (T), then [TOK][E] logits (float)
   T* xs = reinterpret_cast<T*>(route_smem);
@@ -179,12 +180,12 @@ __global__ void route_kernel(const T* __restrict__ x, long x_stride, const float
       continue;
     }
     const float* zt = z + t * E;
-    choose_experts([&](int e) { return zt[e]; }, E, top, eps, lane, ids + (size_t)n * top, weights + (size_t)n * top);
+    choose_experts([&](int e) { return zt[e]; }, E, top, eps, factor, lane, ids + (size_t)n * top, weights + (size_t)n * top);
   }
 }
 
 template <typename T, int TOK>
-int launch_route(const void* x, long x_stride, const float* w, int n_tokens, int E, int K, int top, float eps,
+int launch_route(const void* x, long x_stride, const float* w, int n_tokens, int E, int K, int top, float eps, float factor,
                  const int32_t* req_of_token, int32_t* ids, float* weights, cudaStream_t stream) {
   const size_t smem = (((size_t)TOK * K * sizeof(T) + 15) & ~(size_t)15) + (size_t)TOK * E * sizeof(float);
   if (smem > 200 * 1024) return YALIS_ERR_SHAPE;
@@ -195,7 +196,7 @@ int launch_route(const void* x, long x_stride, const float* w, int n_tokens, int
     configured = smem;
   }
   return yalis_launch(route_kernel<T, TOK>, dim3((n_tokens + TOK - 1) / TOK), dim3(256), smem, stream, (const T*)x, x_stride, w, E, K,
-                      top, eps, req_of_token, ids, weights, n_tokens);
+                      top, eps, factor, req_of_token, ids, weights, n_tokens);
 }
 
 // One block.  entries = n_tokens * top.  tiles: (expert, first slot) per row tile of `bm` slots, ended by n_tiles.
@@ -514,27 +515,27 @@ __global__ void expert_combine_bf16x8_kernel(const __nv_bfloat16* __restrict__ y
 
 }  // namespace
 
-YALIS_API int yalis_route_topk(const float* logits, int n_tokens, int E, int top, float eps, const int32_t* req_of_token,
+YALIS_API int yalis_route_topk(const float* logits, int n_tokens, int E, int top, float eps, float factor, const int32_t* req_of_token,
                                int32_t* ids, float* weights, cudaStream_t stream) {
   if (n_tokens <= 0) return YALIS_OK;
   if (E <= 0 || E > kMaxExperts || top <= 0 || top > kMaxTop || top > E) return YALIS_ERR_SHAPE;
   const int warps = 4;
   return yalis_launch(route_topk_kernel, dim3((n_tokens + warps - 1) / warps), dim3(32 * warps), 0, stream, logits, E, top,
-                      eps, req_of_token, ids, weights, n_tokens);
+                      eps, factor, req_of_token, ids, weights, n_tokens);
 }
 
 // The router and the choice in one launch.  x: [n_tokens, K] float32 or bfloat16; w: float32 [E, K].  Steps of a
 // thousand tokens and more take eight to a block where their rows fit shared memory (fewer tokens would leave SMs
 // without a block: 64 tokens in 8 blocks took 48 us, in 64 blocks 13).
-YALIS_API int yalis_route(const void* x, int x_dtype, long x_stride, const float* w, int n_tokens, int E, int K, int top, float eps,
+YALIS_API int yalis_route(const void* x, int x_dtype, long x_stride, const float* w, int n_tokens, int E, int K, int top, float eps, float factor,
                           const int32_t* req_of_token, int32_t* ids, float* weights, cudaStream_t stream) {
   if (n_tokens <= 0) return YALIS_OK;
   if (E <= 0 || E > kMaxExperts || top <= 0 || top > kMaxTop || top > E || K <= 0) return YALIS_ERR_SHAPE;
   const size_t elt = x_dtype == YALIS_BF16 ? 2 : 4;
   const bool many = n_tokens >= 1024 && 8 * ((size_t)K * elt + (size_t)E * 4) + 16 <= 96 * 1024;
   YALIS_DISPATCH_DTYPE(x_dtype, T,
-                       return many ? launch_route<T, 8>(x, x_stride, w, n_tokens, E, K, top, eps, req_of_token, ids, weights, stream)
-                                   : launch_route<T, 1>(x, x_stride, w, n_tokens, E, K, top, eps, req_of_token, ids, weights, stream));
+                       return many ? launch_route<T, 8>(x, x_stride, w, n_tokens, E, K, top, eps, factor, req_of_token, ids, weights, stream)
+                                   : launch_route<T, 1>(x, x_stride, w, n_tokens, E, K, top, eps, factor, req_of_token, ids, weights, stream));
   return YALIS_OK;
 }
 

@@ -21,6 +21,7 @@ namespace {
 struct LatentPrep {
   const void* src; int src_stride;    // [N, ...] model dtype: heads [plain d | rotated p] at q_off, [c r | k_rot p] at kv_off
   int q_off, kv_off;                  // kv_off < 0: this layer reads another layer's rows and writes none
+  const void* q_src; int q_stride;    // the queries, when they are not columns of src (queries through a latent of their own)
   int heads, d, r, p;
   const float* norm_w; float eps;     // scale of the norm over c
   const float* inv_freq; int rot_dims; int interleaved; float magnitude;   // inv_freq null: no rotation
@@ -62,7 +63,8 @@ __global__ void latent_prepare_kernel(const LatentPrep a) {
   const int pos = a.positions[n];
   const T* row = reinterpret_cast<const T*>(a.src) + (size_t)n * a.src_stride;
   if (job < a.heads) {
-    rotate_part<T, float>(row + a.q_off + (size_t)job * (a.d + a.p) + a.d,
+    const T* qrow = a.q_src ? reinterpret_cast<const T*>(a.q_src) + (size_t)n * a.q_stride : row;
+    rotate_part<T, float>(qrow + a.q_off + (size_t)job * (a.d + a.p) + a.d,
                           a.qc + ((size_t)n * a.heads + job) * (a.r + a.p) + a.r, a.p, pos, a, lane);
     return;
   }
@@ -84,6 +86,26 @@ __global__ void latent_prepare_kernel(const LatentPrep a) {
   const float inv = 1.0f / sqrtf(ss / (float)a.r + a.eps);
   for (int i = lane; i < a.r; i += 32) dst[i] = from_f32<T>(to_f32<T>(s[i]) * inv * a.norm_w[i]);
   rotate_part<T, T>(s + a.r, dst + a.r, a.p, pos, a, lane);
+}
+
+// y[n, :] = x[n, :] / sqrt(mean(x[n, :]^2) + eps) * w for a column block x [N, width] of a wider matrix (the normed
+// latent that queries pass through).  A warp per row; float32 arithmetic, one rounding.
+template <typename T>
+__global__ void norm_rows_kernel(const T* __restrict__ x, long x_stride, const float* __restrict__ w, float eps, int width,
+                                 T* __restrict__ y, long y_stride, int n_rows) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (n >= n_rows) return;
+  const T* s = x + (size_t)n * x_stride;
+  float ss = 0.f;
+  for (int i = lane; i < width; i += 32) {
+    const float v = to_f32<T>(s[i]);
+    ss = __fmaf_rn(v, v, ss);
+  }
+  ss = warp_sum(ss);
+  const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+  for (int i = lane; i < width; i += 32) y[(size_t)n * y_stride + i] = from_f32<T>(to_f32<T>(s[i]) * inv * w[i]);
 }
 
 // ---- per-head linear maps -------------------------------------------------------------------------------------
@@ -149,7 +171,8 @@ __global__ void latent_attention_exact_kernel(const float* __restrict__ qc, floa
                                               const T* __restrict__ pool, const int32_t* __restrict__ positions,
                                               const int32_t* __restrict__ req_of_token,
                                               const int32_t* __restrict__ block_table, int table_width, int page_size,
-                                              int num_pages, int heads, int r, int p, float scale, int window) {
+                                              int num_pages, int heads, int r, int p, float scale, int window,
+                                              const float* __restrict__ sink) {
   extern __shared__ float smem[];   // [kWarps][r] sums, then m[kWarps], l[kWarps]
   pdl_launch_dependents();
   pdl_wait();
@@ -208,7 +231,9 @@ __global__ void latent_attention_exact_kernel(const float* __restrict__ qc, floa
   float mm = -INFINITY;
 #pragma unroll
   for (int k = 0; k < kWarps; ++k) mm = fmaxf(mm, m_s[k]);
-  float ll = 0.f, wgt[kWarps];
+  // a sink is a score of its own in the denominator: no key, no value, not scaled
+  if (sink != nullptr) mm = fmaxf(mm, sink[h]);
+  float ll = sink != nullptr ? expf(sink[h] - mm) : 0.f, wgt[kWarps];
 #pragma unroll
   for (int k = 0; k < kWarps; ++k) {
     wgt[k] = (m_s[k] == -INFINITY) ? 0.f : expf(m_s[k] - mm);
@@ -256,6 +281,7 @@ struct LatentMma {
   const int32_t* positions; const int32_t* q_start;
   const int32_t* block_table; int table_width, page_size, num_pages;
   int heads, p; float scale; int window;
+  const float* sink;                                    // [heads] or null: a score without key and value in every denominator
   int n_splits; float* part_o; float* part_ml;          // [splits, tokens * heads, r] and [.., 2] when n_splits > 1
   int n_tokens;
 };
@@ -510,7 +536,12 @@ __global__ void __launch_bounds__(128 * WR) latent_attention_mma_kernel(const La
         }
         continue;
       }
-      const float inv = l > 0.f ? 1.0f / l : 0.f;
+      float inv = l > 0.f ? 1.0f / l : 0.f;
+      if (a.sink != nullptr) {                      // the sums stand relative to m_run: bring the sink to the same scale
+        const float sk = a.sink[h], mf = fmaxf(m_run[mt][hf], sk);
+        const float c = m_run[mt][hf] == -INFINITY ? 0.f : expf(m_run[mt][hf] - mf);
+        inv = c / (l * c + expf(sk - mf));
+      }
       const size_t base = (size_t)tok * a.o_n + (size_t)h * a.o_h + wc * (R / 4);
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
@@ -531,7 +562,7 @@ __global__ void __launch_bounds__(128 * WR) latent_attention_mma_kernel(const La
 // (token, head): lane z weighs share z, then every column adds its shares in the order of z.
 __global__ void latent_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, int n_splits,
                                     int n_tokens, int heads, int r, const int32_t* __restrict__ req_of_token, void* out,
-                                    int out_bf16, long o_n, long o_h) {
+                                    int out_bf16, long o_n, long o_h, const float* __restrict__ sink) {
   pdl_launch_dependents();
   pdl_wait();
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
@@ -541,9 +572,11 @@ __global__ void latent_merge_kernel(const float* __restrict__ part_o, const floa
   const size_t rows = (size_t)n_tokens * heads;
   const float m = lane < n_splits ? part_ml[((size_t)lane * rows + row) * 2] : -INFINITY;
   const float lz = lane < n_splits ? part_ml[((size_t)lane * rows + row) * 2 + 1] : 0.f;
-  const float M = warp_max(m);
+  float M = warp_max(m);
+  if (sink != nullptr) M = fmaxf(M, sink[h]);
   const float wz = m == -INFINITY ? 0.f : expf(m - M);
-  const float l = warp_sum(lz * wz);
+  float l = warp_sum(lz * wz);
+  if (sink != nullptr) l += expf(sink[h] - M);
   const float inv = l > 0.f ? 1.0f / l : 0.f;
   for (int c = lane; c < r; c += 32) {
     float acc = 0.f;
@@ -593,7 +626,7 @@ YALIS_API int yalis_latent_prepare(const void* src, int dtype, int src_stride, i
                                    int interleaved, float magnitude, float* qc, void* pool,
                                    const int32_t* block_table, int table_width, int page_size, int num_pages,
                                    const int32_t* positions, const int32_t* req_of_token, int n_tokens,
-                                   int32_t* bad_page, cudaStream_t stream) {
+                                   int32_t* bad_page, const void* q_src, int q_stride, cudaStream_t stream) {
   if (n_tokens <= 0) return YALIS_OK;
   if (heads <= 0 || heads > 65535 || d < 0 || r <= 0 || p < 0) return YALIS_ERR_SHAPE;
   if (inv_freq && (rot_dims <= 0 || (rot_dims & 1) || rot_dims > p)) return YALIS_ERR_SHAPE;
@@ -602,10 +635,21 @@ YALIS_API int yalis_latent_prepare(const void* src, int dtype, int src_stride, i
   a.norm_w = norm_w; a.eps = eps; a.inv_freq = inv_freq; a.rot_dims = rot_dims; a.interleaved = interleaved;
   a.magnitude = magnitude; a.qc = qc; a.pool = pool; a.block_table = block_table; a.table_width = table_width;
   a.page_size = page_size; a.num_pages = num_pages; a.positions = positions; a.req_of_token = req_of_token;
-  a.bad_page = bad_page;
+  a.bad_page = bad_page; a.q_src = q_src; a.q_stride = q_stride;
   const int warps = 4;
   const dim3 grid(n_tokens, (heads + 1 + warps - 1) / warps);
   YALIS_DISPATCH_DTYPE(dtype, T, return yalis_launch(latent_prepare_kernel<T>, grid, dim3(32 * warps), 0, stream, a));
+  return YALIS_OK;
+}
+
+YALIS_API int yalis_norm_rows(const void* x, long x_stride, const float* w, float eps, int width, void* y, long y_stride,
+                              int n_rows, int dtype, cudaStream_t stream) {
+  if (n_rows <= 0) return YALIS_OK;
+  if (width <= 0) return YALIS_ERR_SHAPE;
+  const int warps = 4;
+  YALIS_DISPATCH_DTYPE(dtype, T,
+                       return yalis_launch(norm_rows_kernel<T>, dim3((n_rows + warps - 1) / warps), dim3(32 * warps), 0, stream,
+                                           (const T*)x, x_stride, w, eps, width, (T*)y, y_stride, n_rows));
   return YALIS_OK;
 }
 
@@ -650,7 +694,7 @@ YALIS_API int yalis_latent_attention_exact(const float* qc, float* out, const vo
                                            const int32_t* positions, const int32_t* req_of_token,
                                            const int32_t* block_table, int table_width, int page_size, int num_pages,
                                            int n_tokens, int heads, int r, int p, float scale, int window,
-                                           cudaStream_t stream) {
+                                           const float* sink, cudaStream_t stream) {
   if (n_tokens <= 0) return YALIS_OK;
   if (heads <= 0 || heads > 65535 || r <= 0 || p < 0 || r + p > 32 * kMaxPerLane) return YALIS_ERR_SHAPE;
   const size_t smem = ((size_t)kWarps * r + 2 * kWarps) * sizeof(float);
@@ -658,7 +702,7 @@ YALIS_API int yalis_latent_attention_exact(const float* qc, float* out, const vo
   YALIS_DISPATCH_DTYPE(dtype, T,
                        return yalis_launch(latent_attention_exact_kernel<T>, grid, dim3(kWarps * 32), smem, stream, qc, out,
                                            (const T*)pool, positions, req_of_token, block_table, table_width, page_size,
-                                           num_pages, heads, r, p, scale, window));
+                                           num_pages, heads, r, p, scale, window, sink));
   return YALIS_OK;
 }
 
@@ -676,7 +720,8 @@ YALIS_API int yalis_latent_attention_mma(const void* q_lat, int q_lat_bf16, long
                                          const int32_t* positions, const int32_t* q_start, const int32_t* req_of_token,
                                          const int32_t* block_table, int table_width, int page_size, int num_pages,
                                          int n_requests, int n_tokens, int max_q_len, int heads, int r, int p, float scale,
-                                         int window, int n_splits, float* part_o, float* part_ml, cudaStream_t stream) {
+                                         int window, const float* sink, int n_splits, float* part_o, float* part_ml,
+                                         cudaStream_t stream) {
   if (n_requests <= 0 || max_q_len <= 0) return YALIS_OK;
   if (!yalis_latent_attention_mma_supports(r, p) || heads <= 0 || n_requests > 65535 || n_splits < 1 || n_splits > 32)
     return YALIS_ERR_SHAPE;
@@ -686,7 +731,7 @@ YALIS_API int yalis_latent_attention_mma(const void* q_lat, int q_lat_bf16, long
   a.q_lat = q_lat; a.q_lat_bf16 = q_lat_bf16; a.ql_n = ql_n; a.ql_h = ql_h; a.q_rot = q_rot; a.qr_n = qr_n; a.qr_h = qr_h;
   a.out = out; a.out_bf16 = out_bf16; a.o_n = o_n; a.o_h = o_h; a.pool = (const __nv_bfloat16*)pool; a.positions = positions;
   a.q_start = q_start; a.block_table = block_table; a.table_width = table_width; a.page_size = page_size;
-  a.num_pages = num_pages; a.heads = heads; a.p = p; a.scale = scale; a.window = window;
+  a.num_pages = num_pages; a.heads = heads; a.p = p; a.scale = scale; a.window = window; a.sink = sink;
   a.n_splits = n_splits; a.part_o = part_o; a.part_ml = part_ml; a.n_tokens = n_tokens;
   const int max_rows = max_q_len * heads;
   int status = YALIS_ERR_SHAPE;
@@ -701,5 +746,5 @@ YALIS_API int yalis_latent_attention_mma(const void* q_lat, int q_lat_bf16, long
   if (status != YALIS_OK || n_splits == 1) return status;
   const int rows = n_tokens * heads, warps = 4;
   return yalis_launch(latent_merge_kernel, dim3((rows + warps - 1) / warps), dim3(32 * warps), 0, stream, (const float*)part_o,
-                      (const float*)part_ml, n_splits, n_tokens, heads, r, req_of_token, out, out_bf16, o_n, o_h);
+                      (const float*)part_ml, n_splits, n_tokens, heads, r, req_of_token, out, out_bf16, o_n, o_h, sink);
 }

@@ -93,7 +93,7 @@ __global__ void qkv_prepare_kernel(const PrepParams p) {
   for (int d = 2 * half + lane; d < width; d += 32) dst[d] = from_f32<TO>(xs[d] * factor);
 }
 
-// ACT: 0 gelu with erf, 1 gelu with tanh, 2 silu, 3 the square of relu.
+// ACT: 0 gelu with erf, 1 gelu with tanh, 2 silu, 3 the square of relu, 4 tanh.
 template <typename T>
 __global__ void activation_kernel(const T* __restrict__ x, int x_stride, T* __restrict__ y, int y_stride, int rows,
                                   int cols, int act) {
@@ -107,6 +107,7 @@ __global__ void activation_kernel(const T* __restrict__ x, int x_stride, T* __re
     if (act == 0) o = 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f));
     else if (act == 1) o = 0.5f * z * (1.0f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
     else if (act == 2) o = silu_exact(z);
+    else if (act == 4) o = tanhf(z);
     else o = fmaxf(z, 0.f) * fmaxf(z, 0.f);
     y[r * y_stride + c] = from_f32<T>(o);
   }
@@ -118,6 +119,7 @@ __device__ __forceinline__ float act_value(float z, int act) {
   if (act == 0) return 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f));
   if (act == 1) return 0.5f * z * (1.0f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
   if (act == 3) return fmaxf(z, 0.f) * fmaxf(z, 0.f);
+  if (act == 4) return tanhf(z);
   return silu_exact(z);
 }
 
@@ -191,7 +193,7 @@ YALIS_API int yalis_qkv_prepare(const void* src, int dtype, int src_stride, int 
 YALIS_API int yalis_activation(const void* x, int x_stride, void* y, int y_stride, int dtype, int rows, int cols,
                                int act, cudaStream_t stream) {
   if (rows <= 0 || cols <= 0) return YALIS_OK;
-  if (act < 0 || act > 3) return YALIS_ERR_SHAPE;
+  if (act < 0 || act > 4) return YALIS_ERR_SHAPE;
   const size_t total = (size_t)rows * cols;
   const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
   if (dtype == YALIS_BF16 && cols % 8 == 0 && x_stride % 8 == 0 && y_stride % 8 == 0 && !((uintptr_t)x & 15) &&

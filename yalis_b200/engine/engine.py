@@ -160,7 +160,7 @@ class Engine:
         self.max_context = min(ec.max_context or self.spec.max_position, self.spec.max_position)
         self.max_slots = ec.max_slots
         requests = self.model.cache_requests()
-        cache_of = [e.cache_of for e in self.spec.schedule]
+        cache_of = self.model.cache_sources()
         element = 2 if self.dtype == torch.bfloat16 else 4
         page_bytes = sum(group_page_bytes(requests, cache_of, self.page_size, element).values())
         free_bytes = torch.cuda.mem_get_info(self.device)[0] if ec.memory_fraction is not None else None

@@ -24,6 +24,7 @@ class Model:
         self.spec = spec
         self.blocks: List[Block] = [build_block(layer) for layer in spec.layers]
         self.final_norm = make_part("norm", spec.final_norm)
+        self.entry = make_part("entry", spec.entry) if spec.entry is not None else None
         self.embedding: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
         self.dtype: Optional[torch.dtype] = None
@@ -62,6 +63,9 @@ class Model:
                     put(names[slot][local], ps)
         for local, ps in self.final_norm.param_specs().items():
             put(s.final_norm_names[local], ps)
+        if self.entry is not None:
+            for local, ps in self.entry.param_specs().items():
+                put(s.entry_names[local], ps)
         for tensor_name, shape in s.extra_tensors.values():
             put(tensor_name, ParamSpec(tuple(shape), keep_float32=True))
         if s.head_name is not None:
@@ -78,19 +82,30 @@ class Model:
             for slot, part in block.parts.items():
                 part.load({local: fetch(name) for local, name in names[slot].items()})
         self.final_norm.load({local: fetch(s.final_norm_names[local]) for local in self.final_norm.param_specs()})
+        if self.entry is not None:
+            self.entry.load({local: fetch(s.entry_names[local]) for local in self.entry.param_specs()})
         self.head = self.embedding if s.head_name is None else fetch(s.head_name).contiguous()
         self.extra = {local: fetch(tensor_name).contiguous() for local, (tensor_name, _) in s.extra_tensors.items()}
 
     # ---- cache -------------------------------------------------------------------------
     def cache_requests(self) -> List[Optional[object]]:
         """What the block of each schedule entry wants to keep (an entry that reads another
-        entry's cache still says what it expects to find there)."""
-        return [self.blocks[e.layer].cache_request() for e in self.spec.schedule]
+        entry's cache still says what it expects to find there); behind them what the model's entry part keeps,
+        if there is one."""
+        requests = [self.blocks[e.layer].cache_request() for e in self.spec.schedule]
+        if self.entry is not None:
+            requests.append(self.entry.cache_request())
+        return requests
+
+    def cache_sources(self) -> List[Optional[int]]:
+        """For each item of ``cache_requests``: the index of the item whose cache it reads instead of its own."""
+        return [e.cache_of for e in self.spec.schedule] + ([None] if self.entry is not None else [])
 
     def capture_key(self, host):
         """The keys of all parts that run in a step, or ``NOT_CAPTURABLE`` if one of them cannot be recorded."""
         keys = []
-        for part in [self.blocks[i] for i in sorted({e.layer for e in self.spec.schedule})] + [self.final_norm]:
+        parts = [self.blocks[i] for i in sorted({e.layer for e in self.spec.schedule})] + [self.final_norm]
+        for part in parts + ([self.entry] if self.entry is not None else []):
             key = part.capture_key(host)
             if key is NOT_CAPTURABLE:
                 return NOT_CAPTURABLE
@@ -99,11 +114,15 @@ class Model:
 
     # ---- forward -----------------------------------------------------------------------
     def forward(self, ctx, caches: List[Optional[object]], tap: Optional[Callable] = None) -> ResidualStream:
-        """``tap(i, x)``, if given, sees the float32 stream [N, hidden] after schedule entry ``i`` (every pending
-        addition applied): for comparisons layer by layer."""
+        """``tap(i, x)``, if given, sees the float32 stream [N, hidden] (the sum of its copies, if it has several)
+        after schedule entry ``i`` (every pending addition applied): for comparisons layer by layer."""
         x = embedding(self.embedding, ctx.token_ids, bad_flag=ctx.error_flag, scale=self.spec.embedding_scale,
                       from_slot=ctx.token_from_slot, chosen=ctx.chosen if ctx.token_from_slot is not None else None)
+        if self.entry is not None:
+            self.entry.forward(x, ctx, caches[len(self.spec.schedule)])
         entered = x.clone() if self._keeps_embedding else None
+        if self.spec.stream_copies is not None:
+            x = x.unsqueeze(1).repeat(1, self.spec.stream_copies, 1)
         stream = ResidualStream(x, self.dtype)
         for i, (entry, cache) in enumerate(zip(self.spec.schedule, caches)):
             if entry.before is not None:
@@ -111,8 +130,7 @@ class Model:
                 stream.add_rows(entered if b.embedding else None, self.extra[b.vector][b.row] if b.vector is not None else None)
             self.blocks[entry.layer].forward(stream, ctx, cache)
             if tap is not None:
-                stream.flush()
-                tap(i, stream.x)
+                tap(i, stream.total())
         return stream
 
     def logits(self, stream: ResidualStream, rows: torch.Tensor) -> torch.Tensor:
@@ -152,4 +170,5 @@ class Model:
         walk(self.extra)
         walk(self.blocks)
         walk(self.final_norm)
+        walk(self.entry)
         return total

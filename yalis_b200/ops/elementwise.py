@@ -166,14 +166,14 @@ def gather_rows(x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
     return out
 
 
-ACT_GELU_ERF, ACT_GELU_TANH, ACT_SILU, ACT_RELU2 = 0, 1, 2, 3
+ACT_GELU_ERF, ACT_GELU_TANH, ACT_SILU, ACT_RELU2, ACT_TANH = 0, 1, 2, 3, 4
 ACTIVATIONS = {"gelu": ACT_GELU_ERF, "gelu_erf": ACT_GELU_ERF, "gelu_tanh": ACT_GELU_TANH, "silu": ACT_SILU,
-               "relu2": ACT_RELU2}
+               "relu2": ACT_RELU2, "tanh": ACT_TANH}
 
 
 def activation(x: torch.Tensor, kind: str, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """act(x) element by element in float32: ``gelu_erf`` 0.5 z (1 + erf(z / sqrt 2)), ``gelu_tanh``
-    0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))), ``silu`` or ``relu2`` (max(z, 0)^2).  ``x`` and ``out`` are [N, C] with unit inner
+    0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))), ``silu``, ``relu2`` (max(z, 0)^2) or ``tanh``.  ``x`` and ``out`` are [N, C] with unit inner
     stride (column blocks of wider matrices are fine)."""
     name = "activation"
     need_cuda(name, x, out)

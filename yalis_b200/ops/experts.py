@@ -15,9 +15,11 @@ MAX_EXPERTS, MAX_TOP = 1024, 32
 ACT_NONE, ACT_RELU2 = 0, 1
 
 
-def route_topk(logits: torch.Tensor, top: int, eps: float = 1e-20, req_of_token: Optional[torch.Tensor] = None):
+def route_topk(logits: torch.Tensor, top: int, eps: Optional[float] = 1e-20, req_of_token: Optional[torch.Tensor] = None,
+               factor: float = 1.0):
     """(ids int32 [N, top], weights float32 [N, top]): the ``top`` largest of softmax(logits) per row (ties to the
-    smaller index) and those scores divided by their sum + eps.  Rows of no request get ids -1."""
+    smaller index) and those scores divided by their sum + eps (``eps`` None: the scores as they are), times
+    ``factor``.  Rows of no request get ids -1."""
     name = "route_topk"
     need_cuda(name, logits, req_of_token)
     need(logits.dtype == torch.float32 and logits.dim() == 2 and logits.is_contiguous(), name, "logits must be contiguous float32 [N, E]")
@@ -25,12 +27,13 @@ def route_topk(logits: torch.Tensor, top: int, eps: float = 1e-20, req_of_token:
     need(0 < top <= min(e, MAX_TOP) and e <= MAX_EXPERTS, name, f"needs top <= min(E, {MAX_TOP}) and E <= {MAX_EXPERTS}")
     ids = torch.empty((n, top), dtype=torch.int32, device=logits.device)
     weights = torch.empty((n, top), dtype=torch.float32, device=logits.device)
-    check(lib().yalis_route_topk(ptr(logits), i32(n), i32(e), i32(top), f32(eps), ptr(req_of_token), ptr(ids), ptr(weights),
+    check(lib().yalis_route_topk(ptr(logits), i32(n), i32(e), i32(top), f32(-1.0 if eps is None else eps), f32(factor), ptr(req_of_token), ptr(ids), ptr(weights),
                                  stream()), name)
     return ids, weights
 
 
-def route(x: torch.Tensor, router: torch.Tensor, top: int, eps: float = 1e-20, req_of_token: Optional[torch.Tensor] = None):
+def route(x: torch.Tensor, router: torch.Tensor, top: int, eps: Optional[float] = 1e-20, req_of_token: Optional[torch.Tensor] = None,
+          factor: float = 1.0):
     """``route_topk`` of the logits ``x router^T`` in one launch: ``x`` [N, K] (float32 or bfloat16, unit inner stride),
     ``router`` float32 [E, K].  The logits are float32 sums in a fixed order per (token, expert)."""
     name = "route"
@@ -42,7 +45,7 @@ def route(x: torch.Tensor, router: torch.Tensor, top: int, eps: float = 1e-20, r
     ids = torch.empty((n, top), dtype=torch.int32, device=x.device)
     weights = torch.empty((n, top), dtype=torch.float32, device=x.device)
     check(lib().yalis_route(ptr(x), i32(dtype_code(x.dtype)), i64(x.stride(0)), ptr(router), i32(n), i32(e), i32(x.shape[1]), i32(top),
-                            f32(eps), ptr(req_of_token), ptr(ids), ptr(weights), stream()), name)
+                            f32(-1.0 if eps is None else eps), f32(factor), ptr(req_of_token), ptr(ids), ptr(weights), stream()), name)
     return ids, weights
 
 

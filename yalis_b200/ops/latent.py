@@ -13,19 +13,23 @@ from ._lib import check, dtype_code, f32, i32, i64, lib, need, need_cuda, ptr, s
 def latent_prepare(src: torch.Tensor, q_off: int, kv_off: Optional[int], heads: int, d: int, r: int, p: int,
                    norm_w: Optional[torch.Tensor], eps: float, inv_freq: Optional[torch.Tensor], interleaved: bool,
                    magnitude: float, qc: torch.Tensor, pool: Optional[torch.Tensor], block_table: torch.Tensor,
-                   positions: torch.Tensor, req_of_token: torch.Tensor, bad_flag: Optional[torch.Tensor] = None) -> None:
+                   positions: torch.Tensor, req_of_token: torch.Tensor, bad_flag: Optional[torch.Tensor] = None,
+                   q_src: Optional[torch.Tensor] = None) -> None:
     """From the input projection ``src`` [N, ...] (model dtype; per head [d plain | p rotated] from column ``q_off``,
     and from ``kv_off`` the token's [r | p]): writes every head's rotated query part into the last p columns of
     ``qc`` [N, heads, r + p] (float32) and, when ``kv_off`` and ``pool`` are given, the row
     [c / sqrt(mean(c^2) + eps) * norm_w | rotated key part] into the token's place in ``pool``
     [pages, 1, page_size, r + p].  The rotation turns the first 2 * len(inv_freq) of the p sizes by
     position * inv_freq, pairs (2i, 2i + 1) when ``interleaved`` else (i, i + len(inv_freq)), with cosine and sine
-    multiplied by ``magnitude``."""
+    multiplied by ``magnitude``.  With ``q_src`` [N, ...] (dtype of ``src``) the heads' queries are its columns from
+    ``q_off`` instead of columns of ``src``."""
     name = "latent_prepare"
-    need_cuda(name, src, norm_w, inv_freq, qc, pool, block_table, positions, req_of_token, bad_flag)
+    need_cuda(name, src, norm_w, inv_freq, qc, pool, block_table, positions, req_of_token, bad_flag, q_src)
     n = src.shape[0]
     need(src.dim() == 2 and src.stride(1) == 1, name, "src must be [N, ...] with unit inner stride")
-    need(q_off + heads * (d + p) <= src.shape[1] and (kv_off is None or kv_off + r + p <= src.shape[1]), name,
+    qs = src if q_src is None else q_src
+    need(qs.dim() == 2 and qs.stride(1) == 1 and qs.shape[0] == n and qs.dtype == src.dtype, name, "q_src must be [N, ...] like src")
+    need(q_off + heads * (d + p) <= qs.shape[1] and (kv_off is None or kv_off + r + p <= src.shape[1]), name,
          "columns lie outside src")
     need(qc.dtype == torch.float32 and qc.shape == (n, heads, r + p) and qc.is_contiguous(), name,
          "qc must be contiguous float32 [N, heads, r + p]")
@@ -49,7 +53,21 @@ def latent_prepare(src: torch.Tensor, q_off: int, kv_off: Optional[int], heads: 
         ptr(src), i32(dtype_code(src.dtype)), i32(src.stride(0)), i32(q_off), i32(-1 if kv_off is None else kv_off),
         i32(heads), i32(d), i32(r), i32(p), ptr(norm_w), f32(eps), ptr(inv_freq), i32(rot_dims), i32(1 if interleaved else 0),
         f32(magnitude), ptr(qc), ptr(pool if kv_off is not None else None), ptr(block_table), i32(block_table.shape[1]),
-        i32(page_size), i32(num_pages), ptr(positions), ptr(req_of_token), i32(n), ptr(bad_flag), stream()), name)
+        i32(page_size), i32(num_pages), ptr(positions), ptr(req_of_token), i32(n), ptr(bad_flag), ptr(q_src),
+        i32(q_src.stride(0) if q_src is not None else 0), stream()), name)
+
+
+def norm_rows(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """x / sqrt(mean(x^2) + eps) * weight per row of ``x`` [N, width] (a column block of a wider matrix is fine), float32
+    arithmetic; contiguous, in the dtype of ``x``."""
+    name = "norm_rows"
+    need_cuda(name, x, weight)
+    need(x.dim() == 2 and x.stride(1) == 1 and weight.dtype == torch.float32 and weight.shape == (x.shape[1],)
+         and weight.is_contiguous(), name, "x [N, width] with unit inner stride, weight float32 [width]")
+    y = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+    check(lib().yalis_norm_rows(ptr(x), i64(x.stride(0)), ptr(weight), f32(eps), i32(x.shape[1]), ptr(y), i64(y.stride(0)),
+                                i32(x.shape[0]), i32(dtype_code(x.dtype)), stream()), name)
+    return y
 
 
 def head_project(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gate: Optional[torch.Tensor] = None,
@@ -92,11 +110,14 @@ MAX_ROW = 640      # r + p the exact kernel takes
 
 def latent_attention_exact(qc: torch.Tensor, pool: torch.Tensor, positions: torch.Tensor, req_of_token: torch.Tensor,
                            block_table: torch.Tensor, r: int, scale: float, window: Optional[int],
-                           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                           out: Optional[torch.Tensor] = None, sink: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out[n, h, :] = sum_j softmax_j((qc[n, h] . row_j) * scale) row_j[:r] over the rows j of the token's request
-    with 0 <= position - j < window (None: all j <= position).  ``qc`` float32 [N, H, r + p]; float32 [N, H, r]."""
+    with 0 <= position - j < window (None: all j <= position).  ``qc`` float32 [N, H, r + p]; float32 [N, H, r].
+    ``sink`` float32 [H]: exp(sink_h) joins every denominator of head h (a score without key and value, not scaled)."""
     name = "latent_attention_exact"
-    need_cuda(name, qc, pool, positions, req_of_token, block_table, out)
+    need_cuda(name, qc, pool, positions, req_of_token, block_table, out, sink)
+    need(sink is None or (sink.dtype == torch.float32 and sink.shape == (qc.shape[1],) and sink.is_contiguous()), name,
+         "sink must be float32 [H]")
     n, h, w = qc.shape
     need(qc.dtype == torch.float32 and qc.is_contiguous() and 0 < r <= w <= MAX_ROW, name,
          f"qc must be contiguous float32 [N, H, r + p] with r + p <= {MAX_ROW}")
@@ -110,7 +131,7 @@ def latent_attention_exact(qc: torch.Tensor, pool: torch.Tensor, positions: torc
     check(lib().yalis_latent_attention_exact(ptr(qc), ptr(out), ptr(pool), i32(dtype_code(pool.dtype)), ptr(positions),
                                              ptr(req_of_token), ptr(block_table), i32(block_table.shape[1]),
                                              i32(pool.shape[2]), i32(pool.shape[0]), i32(n), i32(h), i32(r), i32(w - r),
-                                             f32(scale), i32(window or 0), stream()), name)
+                                             f32(scale), i32(window or 0), ptr(sink), stream()), name)
     return out
 
 
@@ -121,7 +142,8 @@ def mma_supports(r: int, p: int) -> bool:
 
 def latent_attention_mma(q_lat: torch.Tensor, q_rot: torch.Tensor, out: torch.Tensor, pool: torch.Tensor,
                          positions: torch.Tensor, q_start: torch.Tensor, req_of_token: torch.Tensor, block_table: torch.Tensor,
-                         n_requests: int, max_q_len: int, scale: float, window: Optional[int], n_splits: int = 1) -> torch.Tensor:
+                         n_requests: int, max_q_len: int, scale: float, window: Optional[int], n_splits: int = 1,
+                         sink: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The same sums as ``latent_attention_exact`` on the tensor cores, for bfloat16 rows.  ``q_lat`` [N, H, r]
     (float32 or bfloat16) and ``q_rot`` [N, H, p] (float32) are the two parts of the queries and ``out`` [N, H, r]
     (float32 or bfloat16) the result, each with any strides over n and h and unit inner stride.  ``q_start`` int32
@@ -129,7 +151,9 @@ def latent_attention_mma(q_lat: torch.Tensor, q_rot: torch.Tensor, out: torch.Te
     float32 sums; the weights meet the rows in two bfloat16 halves.  ``n_splits`` > 1 deals the rows a request's
     queries see to that many blocks in turn and merges their shares in order (for steps of single tokens)."""
     name = "latent_attention_mma"
-    need_cuda(name, q_lat, q_rot, out, pool, positions, q_start, req_of_token, block_table)
+    need_cuda(name, q_lat, q_rot, out, pool, positions, q_start, req_of_token, block_table, sink)
+    need(sink is None or (sink.dtype == torch.float32 and sink.shape == (q_lat.shape[1],) and sink.is_contiguous()), name,
+         "sink must be float32 [H]")
     n, h, r = q_lat.shape
     p = q_rot.shape[2]
     need(q_rot.shape == (n, h, p) and out.shape == (n, h, r) and q_rot.dtype == torch.float32
@@ -150,5 +174,5 @@ def latent_attention_mma(q_lat: torch.Tensor, q_rot: torch.Tensor, out: torch.Te
         i64(q_rot.stride(0)), i64(q_rot.stride(1)), ptr(out), i32(out.dtype == torch.bfloat16), i64(out.stride(0)),
         i64(out.stride(1)), ptr(pool), ptr(positions), ptr(q_start), ptr(req_of_token), ptr(block_table), i32(block_table.shape[1]),
         i32(pool.shape[2]), i32(pool.shape[0]), i32(n_requests), i32(n), i32(max_q_len), i32(h), i32(r), i32(p), f32(scale),
-        i32(window or 0), i32(n_splits), ptr(part_o), ptr(part_ml), stream()), name)
+        i32(window or 0), ptr(sink), i32(n_splits), ptr(part_o), ptr(part_ml), stream()), name)
     return out

@@ -114,13 +114,16 @@ def short_conv_silu(x: torch.Tensor, weight: torch.Tensor, slot_rows: torch.Tens
 
 def state_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, slot_rows: torch.Tensor, layout: StateLayout,
                q_start: torch.Tensor, slots: torch.Tensor, *, kv_heads: int, decay: torch.Tensor,
-               beta: Optional[torch.Tensor] = None, max_q_len: int = 0) -> torch.Tensor:
+               beta: Optional[torch.Tensor] = None, unit: Optional[torch.Tensor] = None,
+               removal: Optional[torch.Tensor] = None, max_q_len: int = 0) -> torch.Tensor:
     """Walks every request's tokens in order through the recurrence, from and to the state in its slot.
 
     Per head (S is [dim, vdim]):  S <- g S;  u = beta (v - S^T k) with ``beta`` (the delta rule), else u = v;
     S <- S + k u^T;  o = S^T q.  ``q``, ``k`` float32 [N, kv_heads * dim], ``v`` float32 [N, heads * vdim] (column
     blocks are fine).  ``decay`` float32: [heads] (constant), [N, heads] (per token) or [N, heads * dim] (per key
-    channel too); ``beta`` float32 [N, heads].  ``max_q_len``: the longest portion of the step if known (it bounds
+    channel too); ``beta`` float32 [N, heads].  With ``unit`` and ``removal`` (float32 [N, heads * dim]) the rule is the generalized delta rule instead:
+    S <- diag(g) S - removal (unit^T S) + k v^T, both terms reading the old state; it needs a decay per key channel
+    and kv_heads = heads, and ``decay``, ``unit``, ``removal`` contiguous.  ``max_q_len``: the longest portion of the step if known (it bounds
     the tile of tokens staged in shared memory, nothing else).  Returns float32 [N, heads * vdim]."""
     name = "state_scan"
     need_cuda(name, q, k, v, slot_rows, q_start, slots, decay, beta)
@@ -144,11 +147,19 @@ def state_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, slot_rows: tor
         kind = DECAY_PER_TOKEN if decay.shape[1] == h else DECAY_PER_CHANNEL
     if beta is not None:
         need(beta.dtype == torch.float32 and beta.shape == (n, h) and beta.is_contiguous(), name, "beta must be float32 [N, heads]")
+    rule = 1 if beta is not None else 0
+    if unit is not None or removal is not None:
+        need(beta is None and unit is not None and removal is not None and kind == DECAY_PER_CHANNEL and kv_heads == h, name,
+             "the generalized rule takes unit keys and removal vectors, a decay per key channel, kv_heads = heads and no beta")
+        for t, what in ((unit, "unit"), (removal, "removal")):
+            need(t.dtype == torch.float32 and t.shape == (n, h * d) and t.is_contiguous(), name,
+                 f"{what} must be contiguous float32 [N, heads * dim]")
+        rule = 2
     out = torch.empty((n, h * vd), dtype=torch.float32, device=q.device)
     check(lib().yalis_state_scan(
         ptr(q), i32(q.stride(0)), ptr(k), i32(k.stride(0)), ptr(v), i32(v.stride(0)), ptr(decay), i32(kind), ptr(beta),
-        ptr(slot_rows), i64(slot_rows.stride(0)), ptr(out), i32(out.stride(0)), ptr(q_start), ptr(slots),
-        i32(slots.numel()), i32(h), i32(kv_heads), i32(d), i32(vd), i32(int(beta is not None)), i32(max_q_len), stream()), name)
+        ptr(unit), ptr(removal), ptr(slot_rows), i64(slot_rows.stride(0)), ptr(out), i32(out.stride(0)), ptr(q_start), ptr(slots),
+        i32(slots.numel()), i32(h), i32(kv_heads), i32(d), i32(vd), i32(rule), i32(max_q_len), stream()), name)
     return out
 
 
@@ -164,13 +175,42 @@ def head_norm_gate(o: torch.Tensor, heads: int, vdim: int, eps: float, req_of_to
     n = o.shape[0]
     need(o.dtype == torch.float32 and o.shape == (n, heads * vdim) and o.stride(1) == 1, name, "o must be float32 [N, heads * vdim]")
     need(out.shape == (n, heads * vdim) and out.stride(1) == 1, name, "out must be [N, heads * vdim] with unit inner stride")
+    per_head = False
     if weight is not None:
-        need(weight.dtype == torch.float32 and weight.shape == (vdim,) and weight.is_contiguous(), name, "weight must be float32 [vdim]")
+        need(weight.dtype == torch.float32 and weight.shape in ((vdim,), (heads * vdim,)) and weight.is_contiguous(), name,
+             "weight must be float32 [vdim] or [heads * vdim]")
+        per_head = weight.shape == (heads * vdim,) and heads > 1
     if gate_kind != GATE_NONE:
         need(gate is not None and gate.shape == (n, heads * vdim) and gate.stride(1) == 1 and gate.dtype == out.dtype, name,
              "gate must be [N, heads * vdim] in the output's dtype")
     check(lib().yalis_head_norm_gate(ptr(o), i32(o.stride(0)), ptr(weight), ptr(gate),
                                      i32(gate.stride(0) if gate is not None else 0), i32(gate_kind), ptr(out),
                                      i32(out.stride(0)), i32(dtype_code(out.dtype)), ptr(req_of_token), i32(n), i32(heads),
-                                     i32(vdim), f32(eps), f32(out_scale), stream()), name)
+                                     i32(vdim), f32(eps), f32(out_scale), i32(int(per_head)), stream()), name)
     return out
+
+
+def general_delta_prepare(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, a_raw: torch.Tensor, a_bias: torch.Tensor,
+                          w_raw: torch.Tensor, w_bias: torch.Tensor, heads: int, dim: int, rate: float, unit_eps: float,
+                          req_of_token: torch.Tensor):
+    """What the generalized delta rule reads, six contiguous float32 matrices [N, heads * dim]:
+    (q, k, v, decay, unit, removal) with decay = exp(-rate * sigmoid(w_raw + w_bias)), unit = k / sqrt(sum k^2 +
+    unit_eps) per head and removal = sigmoid(a_raw + a_bias) * unit.  ``q``, ``k``, ``v`` [N, heads * dim] are column
+    blocks of one matrix (one row stride) in the model's dtype, ``a_raw`` and ``w_raw`` [N, heads * dim] in that dtype
+    too; the biases are float32 [heads * dim]."""
+    name = "general_delta_prepare"
+    need_cuda(name, q, k, v, a_raw, a_bias, w_raw, w_bias, req_of_token)
+    n, width = q.shape[0], heads * dim
+    for t in (q, k, v, a_raw, w_raw):
+        need(t.dim() == 2 and t.shape == (n, width) and t.stride(1) == 1 and t.dtype == q.dtype, name,
+             f"q, k, v, a_raw, w_raw must be [N, {width}] of one dtype with unit inner stride")
+    need(q.stride(0) == k.stride(0) == v.stride(0), name, "q, k, v must share a row stride")
+    for t in (a_bias, w_bias):
+        need(t.dtype == torch.float32 and t.shape == (width,) and t.is_contiguous(), name, "biases must be float32 [heads * dim]")
+    need(req_of_token.dtype == torch.int32 and req_of_token.shape == (n,), name, "req_of_token must be int32 [N]")
+    out = torch.empty((6, n, width), dtype=torch.float32, device=q.device)
+    check(lib().yalis_general_delta_prepare(ptr(q), ptr(k), ptr(v), i32(q.stride(0)), ptr(a_raw), i32(a_raw.stride(0)), ptr(a_bias),
+                                            ptr(w_raw), i32(w_raw.stride(0)), ptr(w_bias), f32(rate), f32(unit_eps),
+                                            ptr(req_of_token), i32(n), i32(heads), i32(dim), i32(dtype_code(q.dtype)), ptr(out),
+                                            stream()), name)
+    return tuple(out[i] for i in range(6))

@@ -1,6 +1,6 @@
 """Interfaces of the parts a layer is put together from, and their registry.
 
-Five categories, each with one small interface:
+Seven categories, each with one small interface:
 
 ``norm``          ``forward(stream, rows=None) -> Tensor``: applies the pending
                   residual delta, returns the normed rows in the model dtype.
@@ -11,8 +11,15 @@ Five categories, each with one small interface:
 ``mixer``         ``cache_request() -> PagedKV | SlotState | None`` and
                   ``forward(x, ctx, cache) -> Tensor [N, hidden]``.
 ``feed_forward``  ``forward(x, ctx) -> Tensor [N, hidden]``.
+``connection``    ``write(h, y) -> PendingWrite`` and ``read_weights()``: how a
+                  sub-layer's result enters a stream kept in one or several copies
+                  (factors, a gate computed from the sub-layer's input, the mixing of
+                  the copies) and with which weights the copies are read.
+``entry``         ``cache_request()`` and ``forward(x, ctx, cache) -> None``: what is added
+                  to the token rows as they enter the stream (one per model, optional);
+                  it may keep a state per request like a mixer.
 ``block``         ``forward(stream, ctx, cache) -> None``: the arrangement of the
-                  four above around the residual stream.  A block kind declares the
+                  others around the residual stream.  A block kind declares the
                   places it has (``slots``: place name -> category); a layer's
                   ``LayerSpec.parts`` fills exactly those.
 
@@ -43,7 +50,7 @@ import torch
 
 from yalis_b200.config.spec import PartSpec
 
-CATEGORIES = ("norm", "position", "mixer", "feed_forward", "block")
+CATEGORIES = ("norm", "position", "mixer", "feed_forward", "connection", "entry", "block")
 
 
 @dataclass(frozen=True)
@@ -52,7 +59,7 @@ class ParamSpec:
 
     ``init`` says what the random-weights mode writes: ``normal`` = N(0, 0.02)
     (the reference's GPT._init_weights, yalis/external/model.py:113-120),
-    ``ones`` or ``zeros``.  ``keep_float32``: held in float32 whatever the
+    ``ones``, ``zeros``, ``identity`` (a square matrix) or ``const:<value>``.  ``keep_float32``: held in float32 whatever the
     engine's dtype (norm scales).  ``integer``: an integer table, held as int32.
     """
 
@@ -126,6 +133,24 @@ class SlotStateCache:
 
 # ---- the residual stream ----------------------------------------------------------
 
+@dataclass
+class PendingWrite:
+    """A sub-layer's result on its way into a stream kept in several copies, with everything the write does to it:
+    y <- y * layer_scale * sigmoid(gate + gate_bias), then x_t <- sum_s mix[s, t] x_s + out_weights[t] y.  ``y`` is
+    [N, hidden] or float32 partial sums [P, N, hidden]; every other field may be None (without ``mix``: x_t += y)."""
+
+    y: torch.Tensor
+    gate: Optional[torch.Tensor] = None
+    gate_bias: Optional[torch.Tensor] = None
+    layer_scale: Optional[torch.Tensor] = None
+    mix: Optional[torch.Tensor] = None
+    out_weights: Optional[torch.Tensor] = None
+
+    def arguments(self) -> Dict[str, Optional[torch.Tensor]]:
+        return {"y": self.y, "gate": self.gate, "gate_bias": self.gate_bias, "layer_scale": self.layer_scale, "mix": self.mix,
+                "out_weights": self.out_weights}
+
+
 class ResidualStream:
     """The float32 residual stream [N, hidden] with one pending delta.
 
@@ -133,27 +158,51 @@ class ResidualStream:
     the next norm adds it while it reads the stream (one pass instead of two).
     ``pending`` is [N, hidden] in the model dtype, or float32 split partial sums
     [S, N, hidden] that are added in order.
+
+    A model may keep the stream in several copies: ``x`` is then [N, copies, hidden], what is parked is a
+    ``PendingWrite``, and the norms and arrangements that know such streams read and write all copies in one pass.
     """
 
     def __init__(self, x: torch.Tensor, dtype: torch.dtype):
         self.x = x
         self.dtype = dtype
-        self.pending: Optional[torch.Tensor] = None
+        self.pending = None       # a tensor (see above) or a PendingWrite
 
-    def add(self, delta: torch.Tensor) -> None:
+    @property
+    def copies(self) -> int:
+        return self.x.shape[1] if self.x.dim() == 3 else 1
+
+    def add(self, delta) -> None:
         self.flush()
+        if self.x.dim() == 3 and not isinstance(delta, PendingWrite):
+            raise ValueError("a stream kept in several copies takes a PendingWrite, not a plain sum")
         self.pending = delta
 
     def flush(self) -> None:
-        if self.pending is not None:
+        if self.pending is None:
+            return
+        if isinstance(self.pending, PendingWrite):
+            from yalis_b200.ops.streams import stream_step
+            stream_step(self.x, read=False, **self.pending.arguments())
+        else:
             from yalis_b200.ops.elementwise import residual_add
             residual_add(self.x, self.pending)
-            self.pending = None
+        self.pending = None
+
+    def total(self) -> torch.Tensor:
+        """float32 [N, hidden]: the stream, or the sum of its copies, with what is pending applied."""
+        self.flush()
+        if self.x.dim() == 2:
+            return self.x
+        from yalis_b200.ops.streams import stream_step
+        return stream_step(self.x, out_dtype=torch.float32)
 
     def add_rows(self, other: Optional[torch.Tensor] = None, vector: Optional[torch.Tensor] = None) -> None:
         """x[n, :] += other[n, :] + vector[:] (float32; either may be absent), after what is pending."""
         from yalis_b200.ops.elementwise import add_rows_vector
         self.flush()
+        if self.x.dim() == 3:
+            raise ValueError("rows are added to a stream of one copy only")
         add_rows_vector(self.x, other, vector)
 
 
@@ -242,6 +291,30 @@ class FeedForward(Part):
     category = "feed_forward"
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Connection(Part):
+    category = "connection"
+
+    def read_weights(self) -> Optional[torch.Tensor]:
+        """float32 [copies]: the weights of the stream's copies in the sum a sub-layer reads (None: the plain sum)."""
+        return None
+
+    def write(self, h: torch.Tensor, y: torch.Tensor) -> "PendingWrite":
+        """The sub-layer's result ``y`` (as a mixer or feed-forward returns it) on its way into the stream; ``h`` is
+        what the sub-layer read."""
+        raise NotImplementedError
+
+
+class Entry(Part):
+    category = "entry"
+
+    def cache_request(self):
+        return None
+
+    def forward(self, x: torch.Tensor, ctx, cache) -> None:
+        """Adds to the token rows ``x`` float32 [N, hidden] in place."""
         raise NotImplementedError
 
 
@@ -400,4 +473,4 @@ def registered(category: str) -> Tuple[str, ...]:
 
 
 def _ensure_builtin() -> None:
-    from yalis_b200.parts import attention, block, dense, experts, latent, norm, recurrent, rotary, swiglu  # noqa: F401
+    from yalis_b200.parts import attention, block, dense, entry, experts, hyper, latent, norm, recurrent, rotary, swiglu  # noqa: F401

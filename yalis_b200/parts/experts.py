@@ -4,6 +4,9 @@ router, and optionally a shared one that every token runs.
     s = softmax(W_r x) over all experts (float32);  chosen = the ``top`` largest s;  w_j = s_j / (sum chosen s + eps)
     y = sum_j w_j  D_j act(U_j x)  +  D_s act(U_s x)
 
+With ``renorm`` off the weights are the chosen scores themselves, and ``route_scale`` multiplies them either way.  A
+``gated`` expert has a second input matrix G_j and computes D_j (act(G_j x) * (U_j x)).
+
 The router's matrix is held in float32 and its product, softmax and choice are one float32 kernel.  The experts' products are one
 launch each way over all experts (tokens sorted by expert on the device, nothing read back), so a step with
 routed layers launches the same kernels whatever the routing and can be recorded.
@@ -17,7 +20,7 @@ import torch
 
 from yalis_b200.config.spec import PartSpec
 from yalis_b200.ops import experts as ops
-from yalis_b200.ops.elementwise import ACTIVATIONS, activation
+from yalis_b200.ops.elementwise import ACTIVATIONS, activation, silu_mul
 from yalis_b200.ops.linear import linear
 from .base import FeedForward, ParamSpec, register_part
 
@@ -26,8 +29,10 @@ _GROUPED_ACT = {"relu2": ops.ACT_RELU2, "none": ops.ACT_NONE}
 
 class RoutedExperts(FeedForward):
     """Parameters: ``hidden_size``, ``experts``, ``top``, ``expert_size`` (inner size of an expert), ``activation``
-    (``relu2``: the square of relu), ``shared_size`` (inner size of the shared expert; None: none), ``renorm_eps``
-    (added to the sum of the chosen scores; default 1e-20)."""
+    (``relu2``: the square of relu; ``silu`` with ``gated``), ``gated`` (experts of the form down(act(gate x) * (up x));
+    default False), ``shared_size`` (inner size of the shared expert; None: none), ``renorm`` (divide the chosen scores by
+    their sum; default True), ``renorm_eps`` (added to that sum; default 1e-20), ``route_scale`` (a factor on every
+    weight; default 1)."""
 
     def __init__(self, spec: PartSpec):
         super().__init__(spec)
@@ -36,8 +41,15 @@ class RoutedExperts(FeedForward):
         self.inner = int(p["expert_size"])
         self.act = str(p.get("activation", "relu2"))
         self.shared = int(p["shared_size"]) if p.get("shared_size") is not None else None
-        self.eps = float(p.get("renorm_eps", 1e-20))
-        if self.act not in _GROUPED_ACT or self.act not in ACTIVATIONS:
+        self.eps = float(p.get("renorm_eps", 1e-20)) if bool(p.get("renorm", True)) else None
+        self.route_scale = float(p.get("route_scale", 1.0))
+        self.gated = bool(p.get("gated", False))
+        if self.gated:
+            if self.act != "silu":
+                raise ValueError(f"a gated expert's activation is silu, not {self.act!r}")
+            if self.shared is not None:
+                raise ValueError("a shared expert beside gated experts is not supported")
+        elif self.act not in _GROUPED_ACT or self.act not in ACTIVATIONS:
             raise ValueError(f"activation {self.act!r} is not one the routed feed-forward has ({', '.join(_GROUPED_ACT)})")
         if not 0 < self.top <= min(self.n_experts, ops.MAX_TOP) or self.n_experts > ops.MAX_EXPERTS:
             raise ValueError(f"top {self.top} of {self.n_experts} experts is not supported "
@@ -48,6 +60,8 @@ class RoutedExperts(FeedForward):
     def param_specs(self) -> Dict[str, ParamSpec]:
         specs = {"router": ParamSpec((self.n_experts, self.hidden), keep_float32=True)}
         for i in range(self.n_experts):
+            if self.gated:
+                specs[f"expert_{i}_gate"] = ParamSpec((self.inner, self.hidden))
             specs[f"expert_{i}_up"] = ParamSpec((self.inner, self.hidden))
             specs[f"expert_{i}_down"] = ParamSpec((self.hidden, self.inner))
         if self.shared is not None:
@@ -57,7 +71,11 @@ class RoutedExperts(FeedForward):
 
     def load(self, t: Dict[str, torch.Tensor]) -> None:
         self.router = t["router"].float().contiguous()
-        self.w_up = torch.stack([t[f"expert_{i}_up"] for i in range(self.n_experts)]).contiguous()
+        if self.gated:      # per expert the gate's rows, then the up-projection's: one product, then silu(gate) * up
+            self.w_up = torch.stack([torch.cat([t[f"expert_{i}_gate"], t[f"expert_{i}_up"]], dim=0)
+                                     for i in range(self.n_experts)]).contiguous()
+        else:
+            self.w_up = torch.stack([t[f"expert_{i}_up"] for i in range(self.n_experts)]).contiguous()
         self.w_down = torch.stack([t[f"expert_{i}_down"] for i in range(self.n_experts)]).contiguous()
         if self.shared is not None:
             self.s_up, self.s_down = t["shared_up"].contiguous(), t["shared_down"].contiguous()
@@ -67,7 +85,7 @@ class RoutedExperts(FeedForward):
 
     def matrix_flops_per_token(self) -> float:
         # the products a token runs: the router, ``top`` experts and the shared one
-        return 2.0 * self.hidden * (self.n_experts + 2 * self.top * self.inner + 2 * (self.shared or 0))
+        return 2.0 * self.hidden * (self.n_experts + (3 if self.gated else 2) * self.top * self.inner + 2 * (self.shared or 0))
 
     def expected_unused_bytes(self, tokens: int) -> float:
         """Bytes of the experts that a step of ``tokens`` tokens is expected to leave unread when every choice is
@@ -95,15 +113,21 @@ class RoutedExperts(FeedForward):
         return 128 if entries >= 96 * self.n_experts else (16 if entries <= 8 * self.n_experts else 32)
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
-        ids, weights = ops.route(x, self.router, self.top, self.eps, ctx.req_of_token if ctx is not None else None)
+        ids, weights = ops.route(x, self.router, self.top, self.eps, ctx.req_of_token if ctx is not None else None,
+                                 factor=self.route_scale)
+        act = ops.ACT_NONE if self.gated else _GROUPED_ACT[self.act]
         wstream = self._aligned(x) and ops.wstream_form(x, self.w_up)
         plan = ops.expert_plan(ids, self.n_experts, self.row_tile(x, wstream))
         if wstream:
             rows = ops.gather_rows(x, plan, self.top)
-            inner = ops.grouped_gemm_wstream(rows, self.w_up, plan, act=_GROUPED_ACT[self.act])
+            inner = ops.grouped_gemm_wstream(rows, self.w_up, plan, act=act)
+            if self.gated:
+                inner = silu_mul(inner)
             y = ops.grouped_gemm_wstream(inner, self.w_down, plan)
         else:
-            inner = ops.grouped_gemm(x, self.w_up, plan, gather_top=self.top, act=_GROUPED_ACT[self.act])
+            inner = ops.grouped_gemm(x, self.w_up, plan, gather_top=self.top, act=act)
+            if self.gated:
+                inner = silu_mul(inner)
             y = ops.grouped_gemm(inner, self.w_down, plan)
         shared = None
         if self.shared is not None:

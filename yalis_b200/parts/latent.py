@@ -6,6 +6,9 @@
     o_h(i) = sum_j softmax_j(q_h(i) . key_h(j) * scale) value_h(j)  over the j a window lets i see
     y = W_o (o * sigmoid(W_g x))                (the gate is optional)
 
+Options: the queries may pass through a normed latent of their own (``q_rank``: q = W_uq (W_dq x / rms * n_q)), and
+every head may have a sink, a learned score without key and value whose exponential joins the softmax's denominator.
+
 Only the row [c | k_rot] of a token is cached (one "key head" of width r + p without values).  Keys and values
 are never expanded: U_k,h^T is applied to the plain part of the query and U_v,h to the weighted sum of the
 latents, which turns every head into a query over the same rows (see csrc/latent_attention.cu).  A layer may read
@@ -20,6 +23,7 @@ import torch
 
 from yalis_b200.config.spec import PartSpec
 from yalis_b200.ops import latent as ops
+from yalis_b200.ops.linear import linear
 from .base import Mixer, PagedKV, PagedKVCache, ParamSpec, PositionEncoding, Projected, make_part, register_part, stack_rows
 
 
@@ -28,7 +32,8 @@ class LatentAttention(Mixer, Projected):
     ``rot_dim`` (p, the rotated part), ``v_head_dim`` (e), ``kv_rank`` (r), ``rotary`` (the parameters of a
     ``rotary`` position part whose ``head_dim`` is the number of sizes that turn, at most p; None: no rotation),
     ``scale``, ``window`` (None: all keys), ``cache_window`` (how long rows are kept: at least ``window`` and the
-    windows of the layers that read them; None: for ever), ``norm_eps``, ``gate`` (bool), ``own_latent`` (bool)."""
+    windows of the layers that read them; None: for ever), ``norm_eps``, ``gate`` (bool), ``own_latent`` (bool),
+    ``q_rank`` (size of the queries' latent; None: queries are one product of the input), ``sink`` (bool)."""
 
     def __init__(self, spec: PartSpec, position: Optional[PositionEncoding] = None):
         p = spec.params
@@ -43,6 +48,8 @@ class LatentAttention(Mixer, Projected):
         self.eps = float(p["norm_eps"])
         self.gate = bool(p.get("gate", False))
         self.own = bool(p.get("own_latent", True))
+        self.q_rank = int(p["q_rank"]) if p.get("q_rank") is not None else None
+        self.has_sink = bool(p.get("sink", False))
         if self.r + self.p > ops.MAX_ROW:
             raise ValueError(f"kv_rank + rot_dim = {self.r + self.p} is more than the kernels take ({ops.MAX_ROW})")
         if self.position is not None and self.position.head_dim > self.p:
@@ -53,10 +60,11 @@ class LatentAttention(Mixer, Projected):
         self.w_in: Optional[torch.Tensor] = None
         self.w_out: Optional[torch.Tensor] = None
         self.uk = self.uk_t = self.uv = self.uv_t = self.norm_w = None
+        self.w_uq = self.q_norm_w = self.sink = None
         self.q_off = self.kv_off = self.g_off = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
-        specs = {"q_proj": ParamSpec((self.nh * (self.d + self.p), self.hidden)),
+        specs = {"q_proj": ParamSpec((self.nh * (self.d + self.p), self.hidden if self.q_rank is None else self.q_rank)),
                  "uk_proj": ParamSpec((self.nh * self.d, self.r)), "uv_proj": ParamSpec((self.nh * self.e, self.r)),
                  "o_proj": ParamSpec((self.hidden, self.nh * self.e))}
         if self.own:
@@ -64,10 +72,21 @@ class LatentAttention(Mixer, Projected):
             specs["dkv_norm"] = ParamSpec((self.r,), init="ones", keep_float32=True)
         if self.gate:
             specs["g_proj"] = ParamSpec((self.nh * self.e, self.hidden))
+        if self.q_rank is not None:
+            specs["dq_proj"] = ParamSpec((self.q_rank, self.hidden))
+            specs["dq_norm"] = ParamSpec((self.q_rank,), init="ones", keep_float32=True)
+        if self.has_sink:
+            specs["sink"] = ParamSpec((self.nh,), init="zeros", keep_float32=True)
         return specs
 
     def load(self, t: Dict[str, torch.Tensor]) -> None:
-        blocks, names = [t["q_proj"]], ["q"]
+        if self.q_rank is None:
+            blocks, names = [t["q_proj"]], ["q"]
+        else:       # the input product makes the queries' latent; the queries are a second product of its normed rows
+            blocks, names = [t["dq_proj"]], ["q"]
+            self.w_uq, self.q_norm_w = t["q_proj"].contiguous(), t["dq_norm"].contiguous()
+        if self.has_sink:
+            self.sink = t["sink"].float().contiguous()
         if self.own:
             blocks.append(t["dkv_proj"])
             names.append("kv")
@@ -124,11 +143,15 @@ class LatentAttention(Mixer, Projected):
         freq = pos.frequencies(pos.head_dim, z.device) if pos is not None else None
         table = ctx.block_tables[cache.group]
         qc = torch.empty((n, nh, r + p), dtype=torch.float32, device=z.device)
-        ops.latent_prepare(z, self.q_off, self.kv_off if (self.own and cache.writable) else None, nh, d, r, p, self.norm_w,
+        q_all, q_off = None, self.q_off
+        if self.q_rank is not None:
+            q_all = linear(ops.norm_rows(z[:, self.q_off:self.q_off + self.q_rank], self.q_norm_w, self.eps), self.w_uq)
+            q_off = 0
+        ops.latent_prepare(z, q_off, self.kv_off if (self.own and cache.writable) else None, nh, d, r, p, self.norm_w,
                            self.eps, freq, bool(pos.interleaved) if pos is not None else False,
                            float(pos.magnitude) if pos is not None else 1.0, qc, cache.k, table, ctx.positions,
-                           ctx.req_of_token, bad_flag=ctx.error_flag)
-        q = z[:, self.q_off:self.q_off + nh * (d + p)].unflatten(1, (nh, d + p))
+                           ctx.req_of_token, bad_flag=ctx.error_flag, q_src=q_all)
+        q = (z[:, self.q_off:self.q_off + nh * (d + p)] if q_all is None else q_all).unflatten(1, (nh, d + p))
         gate = z[:, self.g_off:self.g_off + nh * e] if self.gate else None
         if self._tensor_core_form(z.dtype):
             # bfloat16 rows of a shape the tensor-core attention takes: the two per-head maps are batched library
@@ -138,7 +161,7 @@ class LatentAttention(Mixer, Projected):
             mixed = torch.empty((nh, n, r), dtype=z.dtype, device=z.device)
             ops.latent_attention_mma(q_lat.transpose(0, 1), qc[:, :, r:], mixed.transpose(0, 1), cache.k, ctx.positions,
                                      ctx.q_start, ctx.req_of_token, table, ctx.n_requests, ctx.host.max_q_len, self.scale,
-                                     self.window, n_splits=self._splits(ctx))
+                                     self.window, n_splits=self._splits(ctx), sink=self.sink)
             o = torch.bmm(mixed, self.uv_t)                                               # [H, N, e]
             if gate is not None:
                 ops.sigmoid_gate(o.transpose(0, 1), gate, y)
@@ -147,7 +170,7 @@ class LatentAttention(Mixer, Projected):
             return
         # the float32 path, and shapes the tensor-core form does not take: exact kernels throughout
         ops.head_project(q[:, :, :d], self.uk_t, qc[:, :, :r], req_of_token=ctx.req_of_token)
-        mixed = ops.latent_attention_exact(qc, cache.k, ctx.positions, ctx.req_of_token, table, r, self.scale, self.window)
+        mixed = ops.latent_attention_exact(qc, cache.k, ctx.positions, ctx.req_of_token, table, r, self.scale, self.window, sink=self.sink)
         ops.head_project(mixed, self.uv, y.unflatten(1, (nh, e)), gate=gate, req_of_token=ctx.req_of_token)
 
     def forward(self, x: torch.Tensor, ctx, cache: PagedKVCache) -> torch.Tensor:

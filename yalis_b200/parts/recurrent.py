@@ -5,6 +5,9 @@
 ``gated_delta``  S <- g_t S;  u = beta_t (v_t - S^T k_t);  S <- S + k_t u^T;  o_t = S^T q_t  with q, k, v passed
                  through a short causal convolution and silu, q and k brought to unit length, a decay g_t
                  per head or per head and key channel computed from the input, and a normed, gated read-out.
+``general_delta``  S <- diag(w_t) S - (a_t * u_t)(u_t^T S) + k_t v_t^T (both terms read the old S);  o_t = S^T r_t  with
+                 the unit key u_t = k_t / |k_t|, a decay w_t per head and key channel through a low-rank product and a
+                 removal rate a_t per head and key channel; a normed, sigmoid-gated read-out.
 ``sum_of_mixers``  several mixers that read the same input; their results are added, each times its factor.
 
 All three are ``Projected``: an arrangement may run their input and output products together with those of its
@@ -21,7 +24,7 @@ import torch
 
 from yalis_b200.config.spec import PartSpec
 from yalis_b200.ops import recurrent as rec_ops
-from yalis_b200.ops.elementwise import qkv_prepare
+from yalis_b200.ops.elementwise import activation, qkv_prepare
 from yalis_b200.ops.linear import linear
 from .base import Mixer, ParamSpec, PositionEncoding, Projected, SlotState, SlotStateCache, make_part, register_part, stack_rows
 
@@ -195,6 +198,66 @@ class GatedDelta(_ProjectedMixer):
                                gate_kind=kind, out_scale=self.out_scale)
 
 
+class GeneralDelta(_ProjectedMixer):
+    """The generalized delta rule.  Parameters: ``hidden_size``, ``heads``, ``dim`` (of r, k and v alike), ``decay_rank``
+    (rows of the first matrix of the decay's low-rank product), ``decay_rate`` (c in w = exp(-c sigmoid(.))), ``eps`` (of
+    the read-out's norm), ``out_scale``.
+
+        r, k, v = W_r x, W_k x, W_v x            w = exp(-c sigmoid(W_w2 tanh(W_w1 x) + w0))     a = sigmoid(W_a x + b_a)
+        u = k / sqrt(sum k^2 + 1e-6) per head    S <- diag(w) S - (a * u)(u^T S) + k v^T          o = S^T r
+        y = W_o (o / rms(o) per head * n * sigmoid(W_g x))
+
+    Everything between the projections and the output product is float32; the state [heads, dim, dim] is a float32
+    slot row."""
+
+    UNIT_EPS = 1e-6
+
+    def __init__(self, spec: PartSpec, position: Optional[PositionEncoding] = None):
+        super().__init__(spec, position)
+        p = spec.params
+        self.hidden, self.h, self.d = int(p["hidden_size"]), int(p["heads"]), int(p["dim"])
+        self.rank, self.rate, self.eps = int(p["decay_rank"]), float(p["decay_rate"]), float(p["eps"])
+        self.layout = rec_ops.StateLayout(self.h, self.d, self.d)
+        self.hidden_width = self.h * self.d
+        self.spans: Dict[str, tuple] = {}
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        hd, hid = self.h * self.d, self.hidden
+        return {"r_proj": ParamSpec((hd, hid)), "k_proj": ParamSpec((hd, hid)), "v_proj": ParamSpec((hd, hid)),
+                "g_proj": ParamSpec((hd, hid)), "a_proj": ParamSpec((hd, hid)),
+                "a_bias": ParamSpec((hd,), init="zeros", keep_float32=True),
+                "w1_proj": ParamSpec((self.rank, hid)), "w2_proj": ParamSpec((hd, self.rank)),
+                "w_bias": ParamSpec((hd,), init="zeros", keep_float32=True),
+                "norm": ParamSpec((hd,), init="ones", keep_float32=True), "o_proj": ParamSpec((hid, hd))}
+
+    def load(self, t: Dict[str, torch.Tensor]) -> None:
+        rkv = torch.cat([t["r_proj"], t["k_proj"], t["v_proj"]], dim=0)
+        self.w_in, spans = stack_rows([rkv, t["g_proj"], t["a_proj"], t["w1_proj"]])
+        self.spans = dict(zip(("rkv", "g", "a", "w1"), spans))
+        self.w_out = t["o_proj"].contiguous()
+        self.w_w2 = t["w2_proj"].contiguous()
+        self.a_bias, self.w_bias, self.norm_w = t["a_bias"].contiguous(), t["w_bias"].contiguous(), t["norm"].contiguous()
+
+    def cache_request(self) -> SlotState:
+        return SlotState((self.layout.total,), torch.float32)
+
+    def mixing_flops(self, q_len: int, ctx_before: int) -> float:
+        return 8.0 * self.h * self.d * self.d * q_len
+
+    def mix(self, z: torch.Tensor, ctx, cache: SlotStateCache, y: torch.Tensor) -> None:
+        hd = self.h * self.d
+        a0, _ = self.spans["rkv"]
+        blk = lambda name: z[:, self.spans[name][0]:self.spans[name][1]]
+        w_raw = linear(activation(blk("w1"), "tanh"), self.w_w2)
+        q, k, v, decay, unit, removal = rec_ops.general_delta_prepare(
+            z[:, a0:a0 + hd], z[:, a0 + hd:a0 + 2 * hd], z[:, a0 + 2 * hd:a0 + 3 * hd], blk("a"), self.a_bias, w_raw,
+            self.w_bias, self.h, self.d, self.rate, self.UNIT_EPS, ctx.req_of_token)
+        o = rec_ops.state_scan(q, k, v, cache.state, self.layout, ctx.q_start, ctx.slots, kv_heads=self.h, decay=decay,
+                               unit=unit, removal=removal, max_q_len=ctx.host.max_q_len)
+        rec_ops.head_norm_gate(o, self.h, self.d, self.eps, ctx.req_of_token, y, weight=self.norm_w, gate=blk("g"),
+                               gate_kind=rec_ops.GATE_SIGMOID, out_scale=self.out_scale)
+
+
 class SumOfMixers(_ProjectedMixer):
     """Parameters: ``mixers``: name -> PartSpec of a ``Projected`` mixer (its ``out_scale`` is its factor in the sum).
     All read the same input.  Tensors of mixer ``name`` are named ``<name>.<its own name>``; what the mixers keep
@@ -246,4 +309,5 @@ class SumOfMixers(_ProjectedMixer):
 
 register_part("mixer", "retention", Retention)
 register_part("mixer", "gated_delta", GatedDelta)
+register_part("mixer", "general_delta", GeneralDelta)
 register_part("mixer", "sum_of_mixers", SumOfMixers)

@@ -112,6 +112,10 @@ def random_tensor(name: str, ps: ParamSpec, seed: int, device="cpu", std: float 
         return torch.ones(ps.shape, dtype=torch.float32, device=device)
     if ps.init == "zeros":
         return torch.zeros(ps.shape, dtype=torch.float32, device=device)
+    if ps.init == "identity":
+        return torch.eye(ps.shape[0], ps.shape[1], dtype=torch.float32, device=device)
+    if ps.init.startswith("const:"):
+        return torch.full(ps.shape, float(ps.init[6:]), dtype=torch.float32, device=device)
     gen = torch.Generator(device=device)
     gen.manual_seed(_tensor_seed(seed, name))
     return torch.randn(ps.shape, generator=gen, dtype=torch.float32, device=device) * std
