@@ -127,9 +127,31 @@ def latent_attention_mixer(h, t, prefix, m, eps):
     return o.reshape(T, H * e) @ t[prefix + "o"].T
 
 
+def general_delta_rule(r, k, v, w, a, state=None):
+    """r, k, v, w, a [T, H, d].  Per head, with the unit key u_t = k_t / sqrt(sum k_t^2 + 1e-6):
+    S_t = diag(w_t) S_(t-1) - (a_t * u_t)(u_t^T S_(t-1)) + k_t v_t^T (decay and removal both read S_(t-1)),
+    o_t = S_t^T r_t.  Returns (o [T, H, d], the last state [H, d, d]); ``state`` is S before the first token (zeros)."""
+    T, H, d = r.shape
+    u = k / torch.sqrt((k * k).sum(dim=-1, keepdim=True) + 1e-6)
+    out = torch.zeros((T, H, d), dtype=r.dtype)
+    last = torch.zeros((H, d, d), dtype=r.dtype)
+    for hh in range(H):
+        S = torch.zeros((d, d), dtype=r.dtype) if state is None else state[hh].clone()
+        for i in range(T):
+            seen = u[i, hh] @ S                                                       # u^T S_(t-1), one number per value column
+            S = w[i, hh][:, None] * S - torch.outer(a[i, hh] * u[i, hh], seen) + torch.outer(k[i, hh], v[i, hh])
+            out[i, hh] = S.T @ r[i, hh]
+        last[hh] = S
+    return out, last
+
+
+def head_rms(o, eps):
+    """Every head's vector divided by its root mean square (eps inside the root)."""
+    return o / torch.sqrt((o * o).mean(dim=-1, keepdim=True) + eps)
+
+
 def general_delta_mixer(h, t, prefix, m, eps):
-    """S_t = diag(w_t) S_(t-1) - (a_t * u_t)(u_t^T S_(t-1)) + k_t v_t^T,  o_t = S_t^T r_t  per head, u the key
-    brought to unit length; the read-out of each head divided by its root mean square, scaled and gated."""
+    """The rule's inputs from the mixer's input, the rule, and the normed, scaled and gated read-out."""
     T = h.shape[0]
     H, d = m["heads"], m["dim"]
     r = (h @ t[prefix + "r"].T).reshape(T, H, d)
@@ -138,16 +160,8 @@ def general_delta_mixer(h, t, prefix, m, eps):
     low = torch.tanh(h @ t[prefix + "w1"].T) @ t[prefix + "w2"].T + t[prefix + "w0"]
     w = torch.exp(-math.exp(-0.5) * sigmoid(low)).reshape(T, H, d)
     a = sigmoid(h @ t[prefix + "a"].T + t[prefix + "a.b"]).reshape(T, H, d)
-    u = k / torch.sqrt((k * k).sum(dim=-1, keepdim=True) + 1e-6)
-    out = torch.zeros((T, H, d), dtype=h.dtype)
-    for hh in range(H):
-        S = torch.zeros((d, d), dtype=h.dtype)
-        for i in range(T):
-            seen = u[i, hh] @ S                                                       # u^T S_(t-1), [d values]
-            S = w[i, hh][:, None] * S - torch.outer(a[i, hh] * u[i, hh], seen) + torch.outer(k[i, hh], v[i, hh])
-            out[i, hh] = S.T @ r[i, hh]
-    out = out / torch.sqrt((out * out).mean(dim=-1, keepdim=True) + eps)
-    y = out.reshape(T, H * d) * t[prefix + "norm"] * sigmoid(h @ t[prefix + "g"].T)
+    out, _ = general_delta_rule(r, k, v, w, a)
+    y = head_rms(out, eps).reshape(T, H * d) * t[prefix + "norm"] * sigmoid(h @ t[prefix + "g"].T)
     return y @ t[prefix + "o"].T
 
 
@@ -179,15 +193,24 @@ def mixture_of_experts(h, t, prefix, mlp):
 
 # ---- the layer arrangement ------------------------------------------------------------------------
 
+def read_copies(streams, weights):
+    """u = sum_s weights[s] x_s of the copies [S, T, width]."""
+    return torch.einsum("s,stw->tw", weights, streams)
+
+
+def write_copies(streams, mix, out, y):
+    """All copies at once from the old ones: x_t <- sum_s mix[s, t] x_s + out[t] y."""
+    return torch.einsum("sr,stw->rtw", mix, streams) + out[:, None, None] * y[None]
+
+
 def sublayer(streams, t, layer_prefix, q, run):
-    """One sub-layer (q = 1: mixer, 2: feed-forward) between the copies of the stream [S, T, width]:
-    read u = sum_s in_s x_s, y = scale * gate(h) * run(h) with h = norm(u), write x_t <- sum_s mix[s, t] x_s + out_t y."""
+    """One sub-layer (q = 1: mixer, 2: feed-forward) between the copies of the stream [S, T, width]: h = norm(read),
+    y = run(h) * scale * sigmoid(W_g h + b_g), write."""
     hc = f"{layer_prefix}hc{q}."
-    u = torch.einsum("s,stw->tw", t[hc + "in"], streams)
-    h = dynamic_tanh(u, t, f"{layer_prefix}norm{q}")
+    h = dynamic_tanh(read_copies(streams, t[hc + "in"]), t, f"{layer_prefix}norm{q}")
     y = run(h) * t[f"{layer_prefix}ls{q}"]
     y = y * sigmoid(h @ t[f"{layer_prefix}rg{q}"].T + t[f"{layer_prefix}rg{q}.b"])
-    return torch.einsum("sr,stw->rtw", t[hc + "mix"], streams) + t[hc + "out"][:, None, None] * y[None]
+    return write_copies(streams, t[hc + "mix"], t[hc + "out"], y)
 
 
 def layer_order(config):
@@ -204,7 +227,7 @@ def forward(config, t, tokens, dtype=torch.float64, taps=None):
     t = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in t.items()}
     eps = config["norm"]["eps"]
     x = embed_tokens(list(tokens), t, config)
-    streams = x[None].repeat(config["streams"], 1, 1)
+    streams = x[None].repeat(config.get("streams", 1), 1, 1)
     for li in layer_order(config):
         layer, lp = config["layers"][li], f"l{li}."
         m = layer["mixer"]

@@ -220,6 +220,71 @@ PRESETS["vepivik-1b"] = _vepivik_stack(2048, 32000, 4, 16, 8, 128, 256, 64, 1024
 PRESETS["vepivik-3b"] = _vepivik_stack(3072, 32000, 6, 24, 8, 128, 384, 64, 1024, 32, 4, 1536, 3072)
 
 
+# ---- Pametar -------------------------------------------------------------------------------------------------------
+
+def _pm_moe(experts, top, ff, scale):
+    return {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top, "scale": scale}}
+
+
+def _pm_delta(heads, dim, decay_rank, mlp):
+    return {"type": "general_delta", "mixer": {"heads": heads, "dim": dim, "decay_rank": decay_rank}, "mlp": mlp}
+
+
+def _pm_latent(heads, dim, rot_dim, vdim, kv_rank, q_rank, scale, base, mlp):
+    return {"type": "latent_attention", "mlp": mlp,
+            "mixer": {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": kv_rank, "q_rank": q_rank,
+                      "scale": scale, "rot": {"dims": rot_dim, "base": base}}}
+
+
+def _pametar(width, vocab, streams, layers, loop=None, embedding_scale=1.0, bigram=(509, 31, 3), eps=1e-5) -> Dict[str, Any]:
+    emb: Dict[str, Any] = {"scale": embedding_scale}
+    if bigram is not None:
+        emb["bigram"] = {"buckets": bigram[0], "mul_prev": bigram[1], "mul_cur": bigram[2]}
+    cfg = {"architecture": "Pametar", "width": width, "vocab": vocab, "streams": streams, "norm": {"eps": eps},
+           "embedding": emb, "layers": layers}
+    if loop is not None:
+        cfg["loop"] = {"start": loop[0], "stop": loop[1], "times": loop[2]}
+    return cfg
+
+
+def _pametar_stack(width, vocab, groups, streams, heads, dim, kv_rank, q_rank, rot_dim, delta_heads, delta_dim, experts, top, ff):
+    """``groups`` times (generalized delta rule, latent attention) at the sizes of a real model, every layer with experts."""
+    layers = []
+    for _ in range(groups):
+        mlp = _pm_moe(experts, top, ff, 1.0)
+        layers.append(_pm_delta(delta_heads, delta_dim, 64, mlp))
+        layers.append(_pm_latent(heads, dim, rot_dim, dim, kv_rank, q_rank, (dim + rot_dim) ** -0.5, 10000.0, mlp))
+    return _pametar(width, vocab, streams, layers, embedding_scale=width ** 0.5, bigram=(32003, 1009, 31))
+
+
+# Test shapes.  A: two copies of the stream, a looped pair of layers, a layer without feed-forward, one chosen expert.
+# B: sizes that are multiples of nothing, one copy, three passes over one layer, every expert chosen.  C: sizes the
+# tensor-core kernels take, four copies, no loop, no pair table.  D: the rule before attention and after, a loop that
+# covers all layers, three copies, one head, as many latent sizes as query sizes.
+PRESETS["pametar-tiny-A"] = _pametar(64, 96, 2, [
+    _pm_latent(2, 8, 8, 12, 24, 20, 0.3, 100.0, _pm_moe(4, 2, 24, 2.0)),
+    _pm_delta(2, 16, 8, _pm_moe(6, 1, 16, 1.0)),
+    _pm_latent(3, 12, 4, 8, 16, 28, 0.2, 50.0, None),
+    _pm_delta(4, 8, 4, _pm_moe(4, 3, 32, 0.7))], loop=(1, 3, 2), embedding_scale=2.5)
+PRESETS["pametar-tiny-B"] = _pametar(36, 50, 1, [
+    _pm_delta(3, 10, 5, _pm_moe(3, 3, 10, 1.3)),
+    _pm_latent(1, 6, 2, 10, 14, 9, 0.4, 20.0, _pm_moe(5, 3, 18, 1.0)),
+    _pm_delta(1, 20, 3, None)], loop=(0, 1, 3), embedding_scale=0.7, bigram=(7, 5, 11), eps=1e-6)
+PRESETS["pametar-tiny-C"] = _pametar(128, 160, 4, [
+    _pm_latent(4, 32, 32, 32, 64, 48, 0.12, 10000.0, _pm_moe(16, 4, 32, 1.5)),
+    _pm_delta(2, 64, 16, _pm_moe(8, 2, 64, 1.0)),
+    _pm_latent(8, 16, 16, 16, 128, 64, 0.15, 10000.0, _pm_moe(16, 4, 32, 0.5)),
+    _pm_delta(4, 32, 8, _pm_moe(8, 2, 64, 1.0))], embedding_scale=3.0, bigram=None)
+PRESETS["pametar-tiny-D"] = _pametar(48, 64, 3, [
+    _pm_delta(2, 12, 6, _pm_moe(2, 1, 20, 1.0)),
+    _pm_latent(1, 16, 6, 8, 20, 20, 0.25, 7.0, _pm_moe(2, 2, 20, 3.0)),
+    _pm_delta(3, 8, 2, None)], loop=(0, 3, 2), embedding_scale=1.0, bigram=(64, 1, 1))
+# Sizes that resemble a real model's layers (random weights, for the benchmark): the widths, expert counts and latent
+# sizes of the Vepivik benchmark models, so that the two designs stand beside each other at equal size.
+PRESETS["pametar-1b"] = _pametar_stack(2048, 32000, 8, 4, 16, 128, 256, 768, 64, 16, 128, 16, 2, 1280)
+PRESETS["pametar-3b"] = _pametar_stack(3072, 32000, 12, 4, 24, 128, 384, 1024, 64, 24, 128, 32, 4, 1024)
+
+
 def preset(name: str) -> Dict[str, Any]:
     """A fresh copy of the named configuration dictionary."""
     for key in (name, name.split("/")[-1], name.split("/")[-1].replace("Meta-", "")):
