@@ -330,7 +330,7 @@ def test_the_rows_form_of_the_sink_softmax_is_the_plain_attention():
     torch.testing.assert_close(plain_sink_attention(qc, rows, r, 0.4, sink), want)
 
 
-@pytest.mark.parametrize("dtype, r, p, page", [(torch.float32, 24, 8, 16), (torch.float32, 14, 4, 8), (torch.bfloat16, 96, 16, 16),
+@pytest.mark.parametrize("dtype, r, p, page", [(torch.float32, 24, 8, 16), (torch.float32, 14, 4, 8), (torch.bfloat16, 96, 48, 16),
                                                (torch.float32, 20, 2, 64), (torch.bfloat16, 64, 32, 32)])
 def test_the_sink_joins_the_denominator_once_unscaled_and_a_far_row_is_found(dtype, r, p, page):
     """Head 0: a sink that hardly counts; head 1: a sink of the order of the scores; head 2: a sink that takes nearly all
@@ -365,7 +365,7 @@ def test_the_sink_joins_the_denominator_once_unscaled_and_a_far_row_is_found(dty
     assert 0.85 < hit < 1.0 + 1e-6                                                         # exp(24) against exp(2)
 
 
-@pytest.mark.parametrize("r, p, page, heads", [(64, 32, 8, 3), (96, 16, 16, 6), (128, 0, 64, 2), (256, 64, 16, 16), (512, 64, 32, 5)])
+@pytest.mark.parametrize("r, p, page, heads", [(64, 16, 8, 3), (96, 48, 16, 5), (128, 0, 64, 2), (256, 64, 16, 16), (512, 64, 32, 5)])
 @pytest.mark.parametrize("splits", [1, 4])
 def test_the_sink_on_the_tensor_cores(r, p, page, heads, splits):
     """Two requests in one step, a portion behind cached rows beside a single token; with ``splits`` > 1 (a step of
@@ -657,7 +657,7 @@ def random_pametar(rng):
     if rng.random() < 0.7:
         a = rng.randint(0, n - 1)
         loop = (a, rng.randint(a + 1, n), rng.randint(1, 3))
-    bigram = None if rng.random() < 0.2 else (rng.choice([5, 251, 1021, 4099]), rng.randint(0, 200), rng.randint(1, 50))
+    bigram = None if rng.random() < 0.2 else (rng.choice([5, 251, 1019, 4099]), rng.randint(0, 200), rng.randint(1, 50))
     return _pametar(width, rng.choice([80, 300, 700]), rng.randint(1, 4), layers, loop=loop, embedding_scale=rng.choice([1.0, 4.0, 12.0]),
                     bigram=bigram, eps=rng.choice([1e-5, 1e-6]))
 

@@ -33,9 +33,31 @@ struct StreamStep {
   const int32_t* rows; int n_rows;              // rows null: every row, the result of the write is stored
   void* h; long h_stride; int h_f32;            // [n_rows, width] or null
   int store;
+  int vec;                                      // V == 4 only: y, gate, h and the per-column vectors take 8- and 16-byte accesses
 };
 
+// Four consecutive values of a float32 or bfloat16 array as one access (``vec``: 16- resp. 8-byte aligned), else one by one.
 template <int V>
+__device__ __forceinline__ void load_values(const void* base, bool f32, size_t at, bool vec, float (&out)[V]) {
+  if (V == 4 && vec) {
+    if (f32) {
+      const float4 v = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + at);
+      out[0] = v.x; out[1] = v.y; out[V > 1 ? 2 : 0] = v.z; out[V > 1 ? 3 : 0] = v.w;
+    } else {
+      const uint2 v = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(base) + at);
+      const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+      const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+      out[0] = lo.x; out[1] = lo.y; out[V > 1 ? 2 : 0] = hi.x; out[V > 1 ? 3 : 0] = hi.y;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < V; ++j)
+      out[j] = f32 ? reinterpret_cast<const float*>(base)[at + j] : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(base)[at + j]);
+  }
+}
+
+// SC: the number of copies when the launcher knows a kernel for it (1 to 4), else 0: read from the arguments.
+template <int V, int SC>
 __global__ void __launch_bounds__(256) stream_step_kernel(const StreamStep a) {
   pdl_launch_dependents();
   pdl_wait();
@@ -44,7 +66,7 @@ __global__ void __launch_bounds__(256) stream_step_kernel(const StreamStep a) {
   if (n < 0) return;
   const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) * V;
   if (c0 >= a.width) return;
-  const int S = a.copies, D = a.width;
+  const int S = SC ? SC : a.copies, D = a.width;
   float* xr = a.x + (size_t)n * S * D + c0;
   float xs[kMaxCopies][V];
 #pragma unroll
@@ -61,23 +83,35 @@ __global__ void __launch_bounds__(256) stream_step_kernel(const StreamStep a) {
   }
   if (a.y != nullptr) {
     float y[V];
+    if (a.y_f32) {
 #pragma unroll
-    for (int j = 0; j < V; ++j) {
-      float acc = 0.f;
-      if (a.y_f32) {
-        const float* p = reinterpret_cast<const float*>(a.y) + (size_t)n * a.y_stride + c0 + j;
-        for (int q = 0; q < a.y_parts; ++q) acc += p[(size_t)q * a.y_part_stride];
-      } else {
-        acc = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.y)[(size_t)n * a.y_stride + c0 + j]);
+      for (int j = 0; j < V; ++j) y[j] = 0.f;
+      for (int q = 0; q < a.y_parts; ++q) {
+        float part[V];
+        load_values<V>(a.y, true, (size_t)q * a.y_part_stride + (size_t)n * a.y_stride + c0, a.vec, part);
+#pragma unroll
+        for (int j = 0; j < V; ++j) y[j] += part[j];
       }
-      if (a.layer_scale) acc *= a.layer_scale[c0 + j];
-      if (a.gate) {
-        float g = a.gate_f32 ? reinterpret_cast<const float*>(a.gate)[(size_t)n * a.gate_stride + c0 + j]
-                             : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.gate)[(size_t)n * a.gate_stride + c0 + j]);
-        if (a.gate_bias) g += a.gate_bias[c0 + j];
-        acc *= 1.0f / (1.0f + expf(-g));
+    } else {
+      load_values<V>(a.y, false, (size_t)n * a.y_stride + c0, a.vec, y);
+    }
+    if (a.layer_scale) {
+      float sc[V];
+      load_values<V>(a.layer_scale, true, c0, a.vec, sc);
+#pragma unroll
+      for (int j = 0; j < V; ++j) y[j] *= sc[j];
+    }
+    if (a.gate) {
+      float g[V];
+      load_values<V>(a.gate, a.gate_f32, (size_t)n * a.gate_stride + c0, a.vec, g);
+      if (a.gate_bias) {
+        float gb[V];
+        load_values<V>(a.gate_bias, true, c0, a.vec, gb);
+#pragma unroll
+        for (int j = 0; j < V; ++j) g[j] += gb[j];
       }
-      y[j] = acc;
+#pragma unroll
+      for (int j = 0; j < V; ++j) y[j] *= 1.0f / (1.0f + expf(-g[j]));
     }
     if (a.mix == nullptr) {
 #pragma unroll
@@ -136,8 +170,24 @@ __global__ void __launch_bounds__(256) stream_step_kernel(const StreamStep a) {
     }
   if (a.alpha != nullptr) {
     const float al = a.alpha[0];
+    float nw[V], nb[V];
+    load_values<V>(a.norm_w, true, c0, a.vec, nw);
+    load_values<V>(a.norm_b, true, c0, a.vec, nb);
 #pragma unroll
-    for (int j = 0; j < V; ++j) u[j] = __fmaf_rn(tanhf(al * u[j]), a.norm_w[c0 + j], a.norm_b[c0 + j]);
+    for (int j = 0; j < V; ++j) u[j] = __fmaf_rn(tanhf(al * u[j]), nw[j], nb[j]);
+  }
+  if (V == 4 && a.vec) {
+    if (a.h_f32) {
+      *reinterpret_cast<float4*>(reinterpret_cast<float*>(a.h) + (size_t)r * a.h_stride + c0) =
+          make_float4(u[0], u[1], u[V > 1 ? 2 : 0], u[V > 1 ? 3 : 0]);
+    } else {
+      const __nv_bfloat162 lo = __floats2bfloat162_rn(u[0], u[1]), hi = __floats2bfloat162_rn(u[V > 1 ? 2 : 0], u[V > 1 ? 3 : 0]);
+      uint2 v;
+      v.x = *reinterpret_cast<const uint32_t*>(&lo);
+      v.y = *reinterpret_cast<const uint32_t*>(&hi);
+      *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(a.h) + (size_t)r * a.h_stride + c0) = v;
+    }
+    return;
   }
 #pragma unroll
   for (int j = 0; j < V; ++j) {
@@ -212,11 +262,24 @@ YALIS_API int yalis_stream_step(float* x, int n_tokens, int copies, int width, c
   a.norm_w = norm_w; a.norm_b = norm_b; a.rows = rows; a.n_rows = n_rows; a.h = h; a.h_stride = h_stride; a.h_f32 = h_f32;
   a.store = rows == nullptr ? 1 : 0;
   const bool wide = width % 4 == 0 && !((uintptr_t)x & 15);
+  // 8- and 16-byte accesses to everything beside x: every base and row stride must allow them
+  auto fits = [](const void* p, bool f32, long stride) {
+    return p == nullptr || (!((uintptr_t)p & (f32 ? 15 : 7)) && stride % 4 == 0);
+  };
+  a.vec = wide && fits(y, y_f32, y_stride) && (y == nullptr || y_part_stride % 4 == 0) && fits(gate, gate_f32, gate_stride) &&
+          fits(gate_bias, true, 0) && fits(layer_scale, true, 0) && fits(norm_w, true, 0) && fits(norm_b, true, 0) &&
+          fits(h, h_f32, h_stride);
   const int per = wide ? 4 : 1;
   const int threads = 256;
   const dim3 grid((width + threads * per - 1) / (threads * per), count);
-  return wide ? yalis_launch(stream_step_kernel<4>, grid, dim3(threads), 0, stream, a)
-              : yalis_launch(stream_step_kernel<1>, grid, dim3(threads), 0, stream, a);
+  if (!wide) return yalis_launch(stream_step_kernel<1, 0>, grid, dim3(threads), 0, stream, a);
+  switch (copies) {
+    case 1: return yalis_launch(stream_step_kernel<4, 1>, grid, dim3(threads), 0, stream, a);
+    case 2: return yalis_launch(stream_step_kernel<4, 2>, grid, dim3(threads), 0, stream, a);
+    case 3: return yalis_launch(stream_step_kernel<4, 3>, grid, dim3(threads), 0, stream, a);
+    case 4: return yalis_launch(stream_step_kernel<4, 4>, grid, dim3(threads), 0, stream, a);
+    default: return yalis_launch(stream_step_kernel<4, 0>, grid, dim3(threads), 0, stream, a);
+  }
 }
 
 YALIS_API int yalis_pair_rows_add(float* x, int n_tokens, int width, const void* table, int dtype, int buckets,
