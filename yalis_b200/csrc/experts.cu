@@ -129,9 +129,20 @@ __global__ void route_kernel(const T* __restrict__ x, long x_stride, const float
   pdl_wait();
   const int n0 = blockIdx.x * TOK, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
   const int here = min(TOK, n_tokens - n0);
-  for (int i = threadIdx.x; i < TOK * K; i += blockDim.x) {
-    const int t = i / K, k = i - t * K;
-    xs[i] = t < here ? x[(size_t)(n0 + t) * x_stride + k] : from_f32<T>(0.f);
+  constexpr int kPiece = 16 / (int)sizeof(T);       // elements of a 16-byte piece
+  if (K % kPiece == 0 && x_stride % kPiece == 0 && ((uintptr_t)x & 15) == 0) {
+    const int pieces = K / kPiece;
+    for (int i = threadIdx.x; i < TOK * pieces; i += blockDim.x) {
+      const int t = i / pieces, k = (i - t * pieces) * kPiece;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);           // sixteen zero bytes are zeros in both types
+      if (t < here) v = *reinterpret_cast<const uint4*>(x + (size_t)(n0 + t) * x_stride + k);
+      *reinterpret_cast<uint4*>(xs + (size_t)t * K + k) = v;
+    }
+  } else {
+    for (int i = threadIdx.x; i < TOK * K; i += blockDim.x) {
+      const int t = i / K, k = i - t * K;
+      xs[i] = t < here ? x[(size_t)(n0 + t) * x_stride + k] : from_f32<T>(0.f);
+    }
   }
   __syncthreads();
   // four k a lane and load where rows allow it (k = 4 lane + 128 i: one order of sums for every TOK), else one
