@@ -414,7 +414,7 @@ __global__ void general_delta_prepare_kernel(const T* __restrict__ q, const T* _
   if (req_of_token[n] < 0) return;
   const int lane = threadIdx.x & 31, nw = blockDim.x >> 5, width = heads * dim;
   float* row = out + (size_t)n * width;           // six planes [N, width]: q, k, v, decay, unit, removal
-  for (int h = threadIdx.x >> 5; h < heads; h += nw) {
+  for (int h = blockIdx.y * nw + (threadIdx.x >> 5); h < heads; h += nw * gridDim.y) {   // a warp per head
     float ss = 0.f;
     for (int d = lane; d < dim; d += 32) {
       const float kv = to_f32<T>(k[(size_t)n * in_stride + h * dim + d]);
@@ -446,9 +446,11 @@ YALIS_API int yalis_general_delta_prepare(const void* q, const void* k, const vo
                                           cudaStream_t stream) {
   if (n_tokens <= 0) return YALIS_OK;
   if (heads <= 0 || dim <= 0) return YALIS_ERR_SHAPE;
-  const int warps = heads < 8 ? heads : 8;
+  // steps of few tokens: two heads a block, so that a decode step of 8 tokens fills more than 8 SMs
+  const int per_block = n_tokens >= 512 ? 8 : 2;
+  const int warps = heads < per_block ? heads : per_block;
   YALIS_DISPATCH_DTYPE(dtype, T,
-                       return yalis_launch(general_delta_prepare_kernel<T>, dim3(n_tokens), dim3(32 * warps), 0, stream,
+                       return yalis_launch(general_delta_prepare_kernel<T>, dim3(n_tokens, (heads + warps - 1) / warps), dim3(32 * warps), 0, stream,
                                            (const T*)q, (const T*)k, (const T*)v, in_stride, (const T*)a_raw, a_stride, a_bias,
                                            (const T*)w_raw, w_stride, w_bias, rate, unit_eps, req_of_token, heads, dim, out,
                                            (size_t)n_tokens * heads * dim));
