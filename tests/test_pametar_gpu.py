@@ -94,6 +94,22 @@ def test_stream_step_writes_all_copies_from_the_old_ones_and_reads_their_weighte
     # a read alone, unnormed, in bfloat16
     u = stream_step(xd, in_weights=w_in.to(DEV), out_dtype=torch.bfloat16)
     torch.testing.assert_close(u.double().cpu(), plain.read_copies(want_x, w_in.double()), rtol=1e-2, atol=1e-2)
+    # the stream's first pass: all copies are the entering rows, which the pass reads once and stores as copies
+    src = torch.randn(n, width, generator=g)
+    full = src[:, None, :].repeat(1, copies, 1).to(DEV)
+    args = dict(y=y.to(DEV), gate=gate.to(DEV), gate_bias=bias.to(DEV), layer_scale=scale.to(DEV), mix=mix.to(DEV), out_weights=w_out.to(DEV),
+                in_weights=w_in.to(DEV), norm=(alpha.to(DEV), nw.to(DEV), nb.to(DEV)), out_dtype=torch.float32)
+    h_full = stream_step(full, **args)
+    late = torch.full((n, copies, width), float("nan"), device=DEV)
+    h_late = stream_step(late, source=src.to(DEV), **args)
+    assert torch.equal(h_full, h_late) and torch.equal(full, late)
+    late.fill_(float("nan"))
+    only_read = stream_step(late, source=src.to(DEV), in_weights=w_in.to(DEV), out_dtype=torch.float32)        # no write: still stored
+    assert torch.equal(late.cpu(), src[:, None, :].repeat(1, copies, 1))
+    torch.testing.assert_close(only_read.double().cpu(), src.double() * w_in.double().sum(), rtol=1e-5, atol=1e-5)
+    late.fill_(float("nan"))
+    stream_step(late, source=src.to(DEV), rows=i32(rows), out_dtype=torch.float32)                              # chosen rows: nothing stored
+    assert bool(late.isnan().all())
 
 
 def test_one_copy_without_mixing_is_the_plain_residual_sum():

@@ -24,6 +24,7 @@ constexpr int kMaxCopies = 8;
 
 struct StreamStep {
   float* x; int copies; int width;              // [N, copies, width] float32, updated in place when `store`
+  const float* src;                             // [N, width] or null: every copy equals this row (x holds nothing yet)
   const void* y; int y_parts; long y_part_stride; long y_stride; int y_f32;   // [parts][N, width]
   const void* gate; long gate_stride; const float* gate_bias; int gate_f32;  // logits of the gate on y, or null
   const float* layer_scale;                     // [width] or null
@@ -69,6 +70,15 @@ __global__ void __launch_bounds__(256) stream_step_kernel(const StreamStep a) {
   const int S = SC ? SC : a.copies, D = a.width;
   float* xr = a.x + (size_t)n * S * D + c0;
   float xs[kMaxCopies][V];
+  if (a.src != nullptr) {                         // the stream's first pass: all copies are the entering row
+    float e[V];
+    load_values<V>(a.src, true, (size_t)n * D + c0, V == 4, e);
+#pragma unroll
+    for (int s = 0; s < kMaxCopies; ++s)
+      if (s < S)
+#pragma unroll
+        for (int j = 0; j < V; ++j) xs[s][j] = e[j];
+  } else {
 #pragma unroll
   for (int s = 0; s < kMaxCopies; ++s) {
     if (s < S) {
@@ -80,6 +90,7 @@ __global__ void __launch_bounds__(256) stream_step_kernel(const StreamStep a) {
         for (int j = 0; j < V; ++j) xs[s][j] = xr[(size_t)s * D + j];
       }
     }
+  }
   }
   if (a.y != nullptr) {
     float y[V];
@@ -144,18 +155,18 @@ __global__ void __launch_bounds__(256) stream_step_kernel(const StreamStep a) {
 #pragma unroll
           for (int j = 0; j < V; ++j) xs[t][j] = nx[t][j];
     }
-    if (a.store) {
+  }
+  if (a.store && (a.y != nullptr || a.src != nullptr)) {
 #pragma unroll
-      for (int s = 0; s < kMaxCopies; ++s)
-        if (s < S) {
-          if (V == 4) {
-            *reinterpret_cast<float4*>(xr + (size_t)s * D) = make_float4(xs[s][0], xs[s][1], xs[s][V > 1 ? 2 : 0], xs[s][V > 1 ? 3 : 0]);
-          } else {
+    for (int s = 0; s < kMaxCopies; ++s)
+      if (s < S) {
+        if (V == 4) {
+          *reinterpret_cast<float4*>(xr + (size_t)s * D) = make_float4(xs[s][0], xs[s][1], xs[s][V > 1 ? 2 : 0], xs[s][V > 1 ? 3 : 0]);
+        } else {
 #pragma unroll
-            for (int j = 0; j < V; ++j) xr[(size_t)s * D + j] = xs[s][j];
-          }
+          for (int j = 0; j < V; ++j) xr[(size_t)s * D + j] = xs[s][j];
         }
-    }
+      }
   }
   if (a.h == nullptr) return;
   float u[V];
@@ -248,7 +259,8 @@ YALIS_API int yalis_stream_step(float* x, int n_tokens, int copies, int width, c
                                 long y_stride, int y_f32, const void* gate, long gate_stride, const float* gate_bias,
                                 int gate_f32, const float* layer_scale, const float* mix, const float* out_w,
                                 const float* in_w, const float* alpha, const float* norm_w, const float* norm_b,
-                                const int32_t* rows, int n_rows, void* h, long h_stride, int h_f32, cudaStream_t stream) {
+                                const int32_t* rows, int n_rows, void* h, long h_stride, int h_f32, const float* src,
+                                cudaStream_t stream) {
   if (copies < 1 || copies > kMaxCopies || width <= 0) return YALIS_ERR_SHAPE;
   if ((mix == nullptr) != (out_w == nullptr)) return YALIS_ERR_SHAPE;
   if ((alpha == nullptr) != (norm_w == nullptr) || (alpha == nullptr) != (norm_b == nullptr)) return YALIS_ERR_SHAPE;
@@ -256,12 +268,12 @@ YALIS_API int yalis_stream_step(float* x, int n_tokens, int copies, int width, c
   const int count = rows ? n_rows : n_tokens;
   if (count <= 0) return YALIS_OK;
   StreamStep a;
-  a.x = x; a.copies = copies; a.width = width; a.y = y; a.y_parts = y_parts; a.y_part_stride = y_part_stride;
+  a.x = x; a.src = src; a.copies = copies; a.width = width; a.y = y; a.y_parts = y_parts; a.y_part_stride = y_part_stride;
   a.y_stride = y_stride; a.y_f32 = y_f32; a.gate = gate; a.gate_stride = gate_stride; a.gate_bias = gate_bias;
   a.gate_f32 = gate_f32; a.layer_scale = layer_scale; a.mix = mix; a.out_w = out_w; a.in_w = in_w; a.alpha = alpha;
   a.norm_w = norm_w; a.norm_b = norm_b; a.rows = rows; a.n_rows = n_rows; a.h = h; a.h_stride = h_stride; a.h_f32 = h_f32;
   a.store = rows == nullptr ? 1 : 0;
-  const bool wide = width % 4 == 0 && !((uintptr_t)x & 15);
+  const bool wide = width % 4 == 0 && !((uintptr_t)x & 15) && !((uintptr_t)src & 15);
   // 8- and 16-byte accesses to everything beside x: every base and row stride must allow them
   auto fits = [](const void* p, bool f32, long stride) {
     return p == nullptr || (!((uintptr_t)p & (f32 ? 15 : 7)) && stride % 4 == 0);

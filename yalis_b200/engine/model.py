@@ -122,8 +122,11 @@ class Model:
             self.entry.forward(x, ctx, caches[len(self.spec.schedule)])
         entered = x.clone() if self._keeps_embedding else None
         if self.spec.stream_copies is not None:
-            x = x.unsqueeze(1).repeat(1, self.spec.stream_copies, 1)
-        stream = ResidualStream(x, self.dtype)
+            # the copies are stored by the first pass over the stream, which reads the entering rows for all of them
+            copies = torch.empty((x.shape[0], self.spec.stream_copies, x.shape[1]), dtype=torch.float32, device=x.device)
+            stream = ResidualStream(copies, self.dtype, source=x)
+        else:
+            stream = ResidualStream(x, self.dtype)
         for i, (entry, cache) in enumerate(zip(self.spec.schedule, caches)):
             if entry.before is not None:
                 b = entry.before

@@ -18,7 +18,7 @@ def stream_step(x: torch.Tensor, *, y: Optional[torch.Tensor] = None, gate: Opti
                 in_weights: Optional[torch.Tensor] = None,
                 norm: Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = None,
                 rows: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
-                read: bool = True) -> Optional[torch.Tensor]:
+                read: bool = True, source: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
     """One pass over the stream ``x`` float32 [N, S, D] (S copies; [N, D] counts as one copy).
 
     Write, when ``y`` is given ([N, D] in float32 or bfloat16, or float32 partial sums [P, N, D] added in order):
@@ -28,9 +28,12 @@ def stream_step(x: torch.Tensor, *, y: Optional[torch.Tensor] = None, gate: Opti
     ``norm`` = (alpha [1], w [D], b [D]), else h = u; returned as [N, D] in ``out_dtype``.
 
     With ``rows`` (int32 row indices, -1: skip) only those rows are read, into [len(rows), D], and the written copies are
-    not stored: the stream stays as it was."""
+    not stored: the stream stays as it was.
+
+    ``source`` float32 [N, D]: the stream's first pass.  ``x`` holds nothing yet; every copy of row n equals
+    ``source[n]``, and (without ``rows``) the copies are stored to ``x`` whether or not there is a write."""
     name = "stream_step"
-    need_cuda(name, x, y, gate, gate_bias, layer_scale, mix, out_weights, in_weights, rows, *(norm or ()))
+    need_cuda(name, x, y, gate, gate_bias, layer_scale, mix, out_weights, in_weights, rows, source, *(norm or ()))
     need(x.dtype == torch.float32 and x.dim() in (2, 3) and x.is_contiguous(), name, "x must be contiguous float32 [N, S, D] or [N, D]")
     n, d = x.shape[0], x.shape[-1]
     s = x.shape[1] if x.dim() == 3 else 1
@@ -67,13 +70,15 @@ def stream_step(x: torch.Tensor, *, y: Optional[torch.Tensor] = None, gate: Opti
     if read:
         need(out_dtype in (torch.float32, torch.bfloat16), name, "the result is float32 or bfloat16")
         h = torch.empty((count, d), dtype=out_dtype, device=x.device)
-    need(read or y is not None, name, "nothing to do")
+    need(read or y is not None or source is not None, name, "nothing to do")
+    need(source is None or (source.dtype == torch.float32 and source.shape == (n, d) and source.is_contiguous()), name,
+         "source must be contiguous float32 [N, D]")
     check(lib().yalis_stream_step(
         ptr(x), i32(n), i32(s), i32(d), ptr(y), i32(y_parts), i64(y_part_stride), i64(y_stride),
         i32(int(y is not None and y.dtype == torch.float32)), ptr(gate), i64(gate.stride(0) if gate is not None else 0),
         ptr(gate_bias), i32(int(gate is not None and gate.dtype == torch.float32)), ptr(layer_scale), ptr(mix), ptr(out_weights),
         ptr(in_weights), ptr(alpha), ptr(w), ptr(b), ptr(rows), i32(0 if rows is None else rows.numel()), ptr(h),
-        i64(h.stride(0) if h is not None else 0), i32(int(h is not None and h.dtype == torch.float32)), stream()), name)
+        i64(h.stride(0) if h is not None else 0), i32(int(h is not None and h.dtype == torch.float32)), ptr(source), stream()), name)
     return h
 
 

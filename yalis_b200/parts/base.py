@@ -161,12 +161,27 @@ class ResidualStream:
 
     A model may keep the stream in several copies: ``x`` is then [N, copies, hidden], what is parked is a
     ``PendingWrite``, and the norms and arrangements that know such streams read and write all copies in one pass.
+    At the start all copies equal the entering rows: ``source`` [N, hidden] holds them and ``x`` nothing, until the
+    first pass over the stream stores the copies (``take_source`` hands the rows to that pass).
     """
 
-    def __init__(self, x: torch.Tensor, dtype: torch.dtype):
+    def __init__(self, x: torch.Tensor, dtype: torch.dtype, source: Optional[torch.Tensor] = None):
         self.x = x
         self.dtype = dtype
         self.pending = None       # a tensor (see above) or a PendingWrite
+        self.source = source
+
+    def take_source(self, stores: bool = True) -> Optional[torch.Tensor]:
+        """The entering rows, if the copies are not stored yet; ``stores``: the pass that gets them stores the copies."""
+        source = self.source
+        if stores:
+            self.source = None
+        return source
+
+    def materialize(self) -> None:
+        if self.source is not None:
+            from yalis_b200.ops.streams import stream_step
+            stream_step(self.x, source=self.take_source(), read=False)
 
     @property
     def copies(self) -> int:
@@ -183,7 +198,7 @@ class ResidualStream:
             return
         if isinstance(self.pending, PendingWrite):
             from yalis_b200.ops.streams import stream_step
-            stream_step(self.x, read=False, **self.pending.arguments())
+            stream_step(self.x, read=False, source=self.take_source(), **self.pending.arguments())
         else:
             from yalis_b200.ops.elementwise import residual_add
             residual_add(self.x, self.pending)
@@ -195,7 +210,7 @@ class ResidualStream:
         if self.x.dim() == 2:
             return self.x
         from yalis_b200.ops.streams import stream_step
-        return stream_step(self.x, out_dtype=torch.float32)
+        return stream_step(self.x, out_dtype=torch.float32, source=self.take_source())
 
     def add_rows(self, other: Optional[torch.Tensor] = None, vector: Optional[torch.Tensor] = None) -> None:
         """x[n, :] += other[n, :] + vector[:] (float32; either may be absent), after what is pending."""

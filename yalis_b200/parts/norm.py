@@ -33,6 +33,7 @@ class RMSNorm(Norm):
     def forward(self, stream: ResidualStream, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         if stream.copies > 1:
             raise ValueError("rms_norm reads a stream of one copy")
+        stream.materialize()
         if isinstance(stream.pending, PendingWrite):
             stream.flush()
         y = add_rmsnorm(stream.x, stream.pending, self.weight, self.eps, stream.dtype, rows=rows)
@@ -77,7 +78,8 @@ class DynamicTanh(Norm):
         from yalis_b200.ops.streams import stream_step
         pending = stream.pending
         write = pending.arguments() if isinstance(pending, PendingWrite) else ({"y": pending} if pending is not None else {})
-        h = stream_step(stream.x, norm=self.triple(), in_weights=in_weights, rows=rows, out_dtype=stream.dtype, **write)
+        h = stream_step(stream.x, norm=self.triple(), in_weights=in_weights, rows=rows, out_dtype=stream.dtype,
+                        source=stream.take_source(stores=rows is None), **write)
         if rows is None:
             stream.pending = None   # the kernel has stored the written copies
         return h
