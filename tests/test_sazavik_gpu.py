@@ -1,0 +1,548 @@
+"""Sazavik on the GPU against the plain implementation: every mechanism's kernel alone, then whole models cut into
+steps in every way, then generation through the entry point.
+
+Kernel tests build their own index arrays and pages (handed out shuffled) and compare with the functions of
+``plain_sazavik`` in float64.  Where random numbers would hide a fault (a mask that is one position off, a far key
+among hundreds, a sink that is left out) one key is made to stand out.  Model tests make small model folders of four
+configurations that differ in every size and option and replay requests whole, with a decoded tail, in portions down
+to two tokens, and mixed with few pages and slots.
+"""
+
+import json
+import math
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import plain_sazavik as plain
+import traces
+from sazavik_models import sazavik_dir
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def i32(values):
+    return torch.tensor(list(values), dtype=torch.int32, device=DEV)
+
+
+def shuffled_pages(n_tokens, page, seed, spare=3):
+    """(table int32 [1, pages], page id of every token, slot in its page) for one request whose pages lie anywhere."""
+    pages = -(-n_tokens // page)
+    perm = torch.randperm(pages + spare, generator=torch.Generator().manual_seed(seed))[:pages]
+    return perm.to(torch.int32).reshape(1, -1).to(DEV), [int(perm[t // page]) for t in range(n_tokens)], [t % page for t in range(n_tokens)]
+
+
+# ---- heads between the input product and the attention: bias, norm, rotation in both layouts, temperature ---------
+
+@pytest.mark.parametrize("dtype, nq, nk, d, e, dims, interleaved, temp", [
+    (torch.float32, 3, 1, 10, 6, 6, True, None), (torch.float32, 4, 2, 16, 16, 16, False, None),
+    (torch.float32, 2, 2, 12, 20, 0, False, (0.7, 3)), (torch.bfloat16, 4, 2, 64, 64, 32, True, (0.25, 128)),
+    (torch.float32, 2, 1, 8, 8, 2, True, (1.5, 1))])
+def test_heads_are_normed_turned_and_scaled_before_attention(dtype, nq, nk, d, e, dims, interleaved, temp):
+    from yalis_b200.ops.elementwise import qkv_prepare
+    g = torch.Generator().manual_seed(d + dims)
+    page, start, n = 8, 1000, 21                       # positions 1000..1020: angles that a small table would miss
+    table, page_of, slot_of = shuffled_pages(start + n, page, seed=2)
+    q_off, k_off, v_off = 8, 8 + nq * d + 8, 8 + nq * d + 8 + nk * d + 16
+    src = (torch.randn(n, v_off + nk * e + 3, generator=g) * 2).to(dtype)
+    biases = tuple((torch.randn(w, generator=g) * 0.5).to(dtype) for w in (nq * d, nk * d, nk * e))
+    qn, kn = 1 + 0.3 * torch.randn(d, generator=g), 1 + 0.3 * torch.randn(d, generator=g)
+    base = 50.0
+    freq = torch.tensor([base ** (-2.0 * i / dims) for i in range(dims // 2)], dtype=torch.float64).float() if dims else None
+    k_pool = torch.full((table.shape[1] + 3, nk, page, d), 7.0, dtype=dtype, device=DEV)
+    v_pool = torch.full((table.shape[1] + 3, nk, page, e), 7.0, dtype=dtype, device=DEV)
+    positions = torch.arange(start, start + n)
+    q = qkv_prepare(src.to(DEV), (q_off, k_off, v_off), nq, nk, d, e, i32(positions.tolist()), i32([0] * n), out_dtype=dtype,
+                    biases=tuple(b.to(DEV) for b in biases), q_norm=qn.to(DEV), k_norm=kn.to(DEV), norm_eps=1e-3,
+                    inv_freq=None if freq is None else freq.to(DEV), k_pool=k_pool, v_pool=v_pool, block_table=table,
+                    interleaved=interleaved, q_temperature=temp)
+    x = src.double()
+    want_q = plain.head_norm((x[:, q_off:q_off + nq * d] + biases[0].double()).reshape(n, nq, d), qn.double(), 1e-3)
+    want_k = plain.head_norm((x[:, k_off:k_off + nk * d] + biases[1].double()).reshape(n, nk, d), kn.double(), 1e-3)
+    want_v = (x[:, v_off:v_off + nk * e] + biases[2].double()).reshape(n, nk, e)
+    if dims:
+        want_q, want_k = (plain.turn(t, positions, dims, base, interleaved) for t in (want_q, want_k))
+    if temp is not None:
+        want_q = want_q * plain.query_temperature(positions, temp[0], temp[1], torch.float64)[:, None, None]
+    # the angle is a 32-bit product by design: near position 1000 it is known to 6e-5, which values of 2 to 6 carry over
+    tol = dict(rtol=2e-5, atol=5e-4) if dtype == torch.float32 else dict(rtol=1e-2, atol=3e-2)
+    torch.testing.assert_close(q.double().cpu().reshape(n, nq, d), want_q, **tol)
+    got_k = torch.stack([k_pool[page_of[t], :, slot_of[t]] for t in positions.tolist()]).double().cpu()
+    got_v = torch.stack([v_pool[page_of[t], :, slot_of[t]] for t in positions.tolist()]).double().cpu()
+    torch.testing.assert_close(got_k, want_k, **tol)
+    torch.testing.assert_close(got_v, want_v, **tol)
+    untouched = k_pool.clone()
+    for t in positions.tolist():
+        untouched[page_of[t], :, slot_of[t]] = 7.0
+    assert bool((untouched == 7.0).all())                                        # nothing else was written
+    # a mixer that reads another layer's keys writes none
+    before = k_pool.clone()
+    q2 = qkv_prepare(src.to(DEV), (q_off, q_off, q_off), nq, nk, d, e, i32(positions.tolist()), i32([0] * n), out_dtype=dtype,
+                     biases=(biases[0].to(DEV), None, None), q_norm=qn.to(DEV), norm_eps=1e-3,
+                     inv_freq=None if freq is None else freq.to(DEV), k_pool=k_pool, v_pool=v_pool, block_table=table, store=False,
+                     interleaved=interleaved, q_temperature=temp)
+    assert torch.equal(before, k_pool) and torch.equal(q, q2)
+
+
+def test_the_query_temperature_steps_where_the_quotient_does():
+    """coef ln(floor((p + 1) / every) + 1): flat for ``every`` - 1 positions, then a step at p + 1 = every, 2 every, ..."""
+    from yalis_b200.ops.elementwise import qkv_prepare
+    every, coef, n = 7, 0.9, 30
+    src = torch.ones(n, 4, device=DEV)
+    q, _, _ = qkv_prepare(src, (0, 0, 0), 1, 1, 4, 4, i32(range(n)), i32([0] * n), out_dtype=torch.float32,
+                          q_temperature=(coef, every))
+    got = q[:, 0].cpu().tolist()
+    want = [1 + coef * math.log((p + 1) // every + 1) for p in range(n)]
+    assert got == pytest.approx(want, rel=1e-6)
+    assert got[5] == 1.0 and got[6] > 1.3 and got[6] == got[12] and got[13] > got[12]
+
+
+# ---- attention: chunks, windows, sinks, distance bias, gate; page borders, far keys --------------------------------
+
+def plain_row(q, keys, values, scale, pos, mask, size, sink=None, slope=None, gate=None):
+    js = list(plain.visible(pos, mask, size))
+    s = (keys[js] @ q) * scale
+    if slope is not None:
+        s = s - slope * torch.tensor([float(pos - j) for j in js], dtype=torch.float64)
+    m = s.max() if sink is None else torch.maximum(s.max(), sink)
+    e = torch.exp(s - m)
+    denom = e.sum() + (torch.exp(sink - m) if sink is not None else 0.0)
+    out = (e / denom) @ values[js]
+    return out if gate is None else out * torch.sigmoid(gate)
+
+
+def attention_case(dtype, hs, vd, page, n, heads, kv_heads, seed):
+    g = torch.Generator().manual_seed(seed)
+    table, page_of, slot_of = shuffled_pages(n, page, seed=seed)
+    keys = torch.randn(n, kv_heads, hs, generator=g).to(dtype)
+    values = torch.randn(n, kv_heads, vd, generator=g).to(dtype)
+    k_pool = torch.full((table.shape[1] + 3, kv_heads, page, hs), float("nan"), dtype=dtype, device=DEV)
+    v_pool = torch.full((table.shape[1] + 3, kv_heads, page, vd), float("nan"), dtype=dtype, device=DEV)
+    for t in range(n):
+        k_pool[page_of[t], :, slot_of[t]] = keys[t].to(DEV)
+        v_pool[page_of[t], :, slot_of[t]] = values[t].to(DEV)
+    return g, table, keys, values, k_pool, v_pool
+
+
+@pytest.mark.parametrize("dtype, hs, vd, page, mask, size", [
+    (torch.float32, 12, 20, 16, "chunk", 9), (torch.bfloat16, 56, 24, 16, "chunk", 45), (torch.float32, 8, 8, 8, "chunk", 64),
+    (torch.float32, 16, 16, 64, "chunk", 1), (torch.float32, 12, 20, 16, "window", 9), (torch.bfloat16, 64, 64, 16, "chunk", 48),
+    (torch.bfloat16, 64, 64, 16, "window", 37), (torch.bfloat16, 96, 96, 8, "chunk", 100), (torch.bfloat16, 48, 48, 64, "window", 1)])
+def test_attention_sees_exactly_its_chunk_or_window(dtype, hs, vd, page, mask, size):
+    """One key is made to stand out.  Queries that see it answer with its value; the query just before it, the first
+    query of the next chunk (or the first one past the window) and all later ones do not.  Run once with all queries
+    in one portion and once with each as a single decoded token; the tensor-core kernel where the shape allows it."""
+    from yalis_b200.ops.attention import mma_supports, paged_attention_generic, paged_attention_mma
+    n, heads, kv_heads = 260, 4, 2
+    g, table, keys, values, k_pool, v_pool = attention_case(dtype, hs, vd, page, n, heads, kv_heads, seed=hs + size)
+    star = 131
+    q = torch.randn(n, heads, hs, generator=g).to(dtype)
+    direction = torch.randn(hs, generator=g)
+    direction /= direction.norm()
+    keys = keys.clone()
+    keys[star] = (direction * 30).to(dtype)                           # q . k of about 30 |q_parallel|
+    q = (q + 3 * direction.to(dtype)).to(dtype)
+    for slot in range(kv_heads):
+        k_pool[int(table[0, star // page]), slot, star % page] = keys[star, slot].to(DEV)
+    scale = 0.5
+    sink = torch.tensor([0.5, -1.0, 2.0, 0.0])
+    slopes = torch.tensor([0.5, 0.25, 0.1, 0.02]) if mask == "window" else None
+    gate = torch.randn(n, heads * vd, generator=g).to(dtype)
+    want = torch.stack([torch.stack([plain_row(q[t, h].double(), keys[:, h // 2].double(), values[:, h // 2].double(), scale, t, mask,
+                                               size, sink=sink[h].double(), slope=None if slopes is None else float(slopes[h]),
+                                               gate=gate[t, h * vd:(h + 1) * vd].double()) for h in range(heads)]) for t in range(n)])
+    # the oracle itself must show the edge: the starred key carries the answer inside, none of it outside
+    last_in = (star // size) * size + size - 1 if mask == "chunk" else star + size - 1
+    kwargs = dict(scale=scale, window=size if mask == "window" else None, chunk=size if mask == "chunk" else None, sink=True,
+                  sink_logits=sink.to(DEV), slopes=None if slopes is None else slopes.to(DEV))
+    positions, reqs = i32(range(n)), i32([0] * n)
+    qd = q.reshape(n, heads * hs).to(DEV)
+    tol = dict(rtol=1e-4, atol=1e-4) if dtype == torch.float32 else dict(rtol=3e-2, atol=3e-2)
+    got = paged_attention_generic(qd, k_pool, v_pool, positions, reqs, table, heads, kv_heads, hs, v_head_dim=vd,
+                                  gate=gate.to(DEV), **kwargs).double().cpu().reshape(n, heads, vd)
+    torch.testing.assert_close(got, want, **tol)
+    for t in (star - 1, star, min(last_in, n - 1), min(last_in + 1, n - 1)):          # each alone, as a decoded token
+        one = paged_attention_generic(qd[t:t + 1], k_pool, v_pool, i32([t]), i32([0]), table, heads, kv_heads, hs, v_head_dim=vd,
+                                      gate=gate[t:t + 1].to(DEV), **kwargs).double().cpu().reshape(heads, vd)
+        torch.testing.assert_close(one, want[t], **tol)
+    if dtype == torch.bfloat16 and hs == vd and mma_supports(hs):
+        q_start = i32([0, n])
+        got = paged_attention_mma(qd, k_pool, v_pool, positions, q_start, reqs, table, n, heads, kv_heads, hs, exact_weights=True,
+                                  gate=gate.to(DEV), **kwargs).double().cpu().reshape(n, heads, vd)
+        torch.testing.assert_close(got, want, **tol)
+        for t in (star - 1, star, min(last_in, n - 1), min(last_in + 1, n - 1), n - 1):
+            for splits in (1, 3):
+                one = paged_attention_mma(qd[t:t + 1].contiguous(), k_pool, v_pool, i32([t]), i32([0, 1]), i32([0]), table, 1, heads,
+                                          kv_heads, hs, exact_weights=True, n_splits=splits, gate=gate[t:t + 1].to(DEV).contiguous(),
+                                          **kwargs).double().cpu().reshape(heads, vd)
+                torch.testing.assert_close(one, want[t], **tol)
+    # inside the edge the starred value dominates an ungated, sinkless answer; outside it is gone
+    plain_kwargs = dict(kwargs, sink=False, sink_logits=None, slopes=None)
+    free = paged_attention_generic(qd, k_pool, v_pool, positions, reqs, table, heads, kv_heads, hs, v_head_dim=vd,
+                                   **plain_kwargs).double().cpu().reshape(n, heads, vd)
+    near = lambda t: float((free[t, 0] - values[star, 0].double()).abs().max())
+    if last_in < n - 1 and last_in > star:
+        assert near(star) < 0.1 and near(last_in) < 0.1 and near(last_in + 1) > 0.3 and near(star - 1) > 0.3
+
+
+def test_a_far_key_among_hundreds_and_a_sink_that_takes_the_weight():
+    """Position 3 of 700 stands out; a query at the end of an unmasked, unchunked sequence finds it.  With a sink
+    score far above every key's the answer is nearly nothing."""
+    from yalis_b200.ops.attention import paged_attention_generic, paged_attention_mma
+    n, heads, kv_heads, hs = 700, 2, 1, 64
+    g, table, keys, values, k_pool, v_pool = attention_case(torch.bfloat16, hs, hs, 16, n, heads, kv_heads, seed=5)
+    q = torch.randn(1, heads * hs, generator=g).to(torch.bfloat16)
+    keys[3, 0] = (q[0, :hs].float() * 4).to(torch.bfloat16)
+    k_pool[int(table[0, 0]), 0, 3] = keys[3, 0].to(DEV)
+    args = (k_pool, v_pool, i32([n - 1]), i32([0]), table, heads, kv_heads, hs)
+    for sink_value, check in ((-30.0, lambda o: float((o[0, :hs] - values[3, 0].double()).abs().max()) < 0.05),
+                              (400.0, lambda o: float(o.abs().max()) < 1e-3)):
+        sink = torch.full((heads,), sink_value, device=DEV)
+        exact = paged_attention_generic(q.to(DEV), *args, scale=0.5, sink=True, sink_logits=sink).double().cpu()
+        fast = paged_attention_mma(q.to(DEV), k_pool, v_pool, i32([n - 1]), i32([0, 1]), i32([0]), table, 1, heads, kv_heads, hs,
+                                   scale=0.5, sink=True, sink_logits=sink, n_splits=4).double().cpu()
+        assert check(exact) and check(fast)
+        torch.testing.assert_close(exact, fast, rtol=2e-2, atol=2e-2)
+
+
+def test_unequal_requests_in_one_launch_each_as_alone():
+    """Three requests of unequal lengths in one launch (a long portion across several chunks, a single token, a short
+    portion that starts in the middle of a chunk), pages interleaved: every row equals the request run alone."""
+    from yalis_b200.ops.attention import paged_attention_generic, paged_attention_mma
+    from ctx_helper import make_context
+    heads, kv_heads, hs, page, chunk = 4, 2, 64, 16, 40
+    q_lens, before = [90, 1, 13], [7, 203, 70]
+    ctx, num_pages = make_context(q_lens, before, page, seed=4)
+    g = torch.Generator().manual_seed(8)
+    k_pool = torch.randn(num_pages, kv_heads, page, hs, generator=g).to(torch.bfloat16).to(DEV)
+    v_pool = torch.randn(num_pages, kv_heads, page, hs, generator=g).to(torch.bfloat16).to(DEV)
+    q = torch.randn(sum(q_lens), heads * hs, generator=g).to(torch.bfloat16).to(DEV)
+    sink = torch.randn(heads, generator=g).to(DEV)
+    table = ctx.block_tables["kv_all"]
+    kw = dict(scale=0.2, chunk=chunk, sink=True, sink_logits=sink)
+    exact = paged_attention_generic(q, k_pool, v_pool, ctx.positions, ctx.req_of_token, table, heads, kv_heads, hs, **kw)
+    fast = paged_attention_mma(q, k_pool, v_pool, ctx.positions, ctx.q_start, ctx.req_of_token, table, max(q_lens), heads, kv_heads, hs,
+                               exact_weights=True, **kw)
+    torch.testing.assert_close(exact.float(), fast.float(), rtol=2e-2, atol=2e-2)
+    at = 0
+    for r, (ql, b) in enumerate(zip(q_lens, before)):
+        alone = paged_attention_mma(q[at:at + ql].contiguous(), k_pool, v_pool, i32(range(b, b + ql)), i32([0, ql]), i32([0] * ql),
+                                    table[r:r + 1].contiguous(), ql, heads, kv_heads, hs, exact_weights=True, **kw)
+        # the same tiles in the same order: the same bits
+        assert torch.equal(alone, fast[at:at + ql]), r
+        at += ql
+
+
+# ---- the stream's norms: a result normed on its way in, token rows normed as they enter ----------------------------
+
+@pytest.mark.parametrize("width, parts, dtype", [(48, 1, torch.float32), (200, 3, torch.float32), (1024, 1, torch.bfloat16), (37, 2, torch.float32)])
+def test_a_result_normed_before_it_joins_the_stream(width, parts, dtype):
+    from yalis_b200.ops.elementwise import add_normed_rmsnorm
+    g = torch.Generator().manual_seed(width)
+    n = 9
+    x = torch.randn(n, width, generator=g)
+    delta = torch.randn(parts, n, width, generator=g) * 3 if parts > 1 else (torch.randn(n, width, generator=g) * 3).to(dtype)
+    bias, wd, w = (torch.randn(width, generator=g) * 0.3 for _ in range(3))
+    d = (delta.double().sum(0) if parts > 1 else delta.double()) + bias.double()
+    want_x = x.double() + plain.rms(d, 1e-4) * (1 + wd.double())
+    want_y = plain.rms(want_x, 1e-5) * (1 + w.double())
+    xs = x.clone().to(DEV)
+    y = add_normed_rmsnorm(xs, delta.to(DEV), bias=bias.to(DEV), delta_norm=((1 + wd).to(DEV), 1e-4), weight=(1 + w).to(DEV), eps=1e-5,
+                           out_dtype=dtype)
+    torch.testing.assert_close(xs.double().cpu(), want_x, rtol=1e-5, atol=1e-5)
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    torch.testing.assert_close(y.double().cpu(), want_y, rtol=tol, atol=tol)
+    # some rows only: the stream stays as it is
+    xs2 = x.clone().to(DEV)
+    rows = add_normed_rmsnorm(xs2, delta.to(DEV), bias=bias.to(DEV), delta_norm=((1 + wd).to(DEV), 1e-4), weight=(1 + w).to(DEV),
+                              eps=1e-5, out_dtype=dtype, rows=i32([7, 2]))
+    assert torch.equal(xs2.cpu(), x) and torch.equal(rows, y[[7, 2]])
+    # no norm on the result and none behind it: a plain sum with a bias
+    xs3 = x.clone().to(DEV)
+    assert add_normed_rmsnorm(xs3, delta.to(DEV), bias=bias.to(DEV)) is None
+    torch.testing.assert_close(xs3.double().cpu(), x.double() + d, rtol=1e-6, atol=1e-6)
+
+
+def test_token_rows_are_normed_as_they_enter():
+    from yalis_b200.ops.elementwise import embedding
+    g = torch.Generator().manual_seed(1)
+    table = torch.randn(30, 52, generator=g).to(torch.bfloat16)
+    w = torch.randn(52, generator=g) * 0.2
+    ids = [4, 29, 0, 4]
+    got = embedding(table.to(DEV), i32(ids), norm=((1 + w).to(DEV), 1e-3))
+    want = plain.stream_norm(table.double()[ids], w.double(), 1e-3)
+    assert got.dtype == torch.float32
+    torch.testing.assert_close(got.double().cpu(), want, rtol=1e-5, atol=1e-5)
+
+
+# ---- feed-forwards ---------------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_the_clamped_gated_activation(dtype):
+    from yalis_b200.ops.elementwise import GATED_CLAMPED, gated_activation
+    g = torch.Generator().manual_seed(2)
+    n, inner, limit = 11, 40, 1.25
+    z = (torch.randn(n, 5 + 2 * inner, generator=g) * 2).to(dtype)           # values on both sides of the limit
+    out = gated_activation(z.to(DEV), 5, 5 + inner, inner, kind=GATED_CLAMPED, limit=limit, alpha=1.702, shift=1.0)
+    gate = torch.clamp(z[:, 5:5 + inner].double(), max=limit)
+    up = torch.clamp(z[:, 5 + inner:].double(), min=-limit, max=limit)
+    want = gate * torch.sigmoid(1.702 * gate) * (up + 1)
+    assert float(gate.max()) == limit and float(up.min()) == -limit and float(gate.min()) < -limit          # the gate has no floor
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    torch.testing.assert_close(out.double().cpu(), want, rtol=tol, atol=tol)
+
+
+def ff_tensors(hidden, experts, inner, shared, seed, dtype):
+    g = torch.Generator().manual_seed(seed)
+    r = lambda *s: (torch.randn(*s, generator=g) * (2.0 / s[-1] ** 0.5)).to(torch.bfloat16).float()
+    t = {"router": r(experts, hidden) * 3}
+    for e in range(experts):
+        t.update({f"e{e}.gate": r(inner, hidden), f"e{e}.up": r(inner, hidden), f"e{e}.down": r(hidden, inner)})
+    if shared:
+        t.update({"shared.gate": r(shared, hidden), "shared.up": r(shared, hidden), "shared.down": r(hidden, shared),
+                  "shared.sg": r(1, hidden) * 3})
+    return t
+
+
+@pytest.mark.parametrize("n, experts, top", [(50, 8, 3), (7, 5, 5), (33, 64, 6), (4, 3, 1), (20, 130, 8)])
+def test_the_sigmoid_router_against_the_plain_one(n, experts, top):
+    from yalis_b200.ops.experts import route
+    g = torch.Generator().manual_seed(n)
+    hidden = 24
+    x = torch.randn(n, hidden, generator=g)
+    w = torch.randn(experts, hidden, generator=g)
+    w[:, 0] += 40.0 * (torch.arange(experts) % 3 == 0)              # some logits past where a float32 sigmoid is 1
+    side = torch.randn(hidden, generator=g)
+    ids, weights, gate = route(x.to(DEV), w.to(DEV), top, None, i32([0] * n), score="sigmoid", side=side.to(DEV))
+    want_ids, want_w = plain.route(x.double(), {"router": w.double()}, "", top)
+    z = x.double() @ w.double().T
+    for row in range(n):                                             # the choice follows the logits, also among saturated scores
+        order = sorted(range(experts), key=lambda e: (-float(z[row, e]), e))[:top]
+        assert ids[row].tolist() == order
+    torch.testing.assert_close(weights.double().cpu(), torch.sigmoid(torch.gather(z, 1, ids.long().cpu())), rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(gate.double().cpu(), torch.sigmoid(x.double() @ side.double()), rtol=1e-5, atol=1e-6)
+    del want_ids, want_w
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n, hidden, experts, top, inner, shared", [
+    (40, 64, 6, 2, 24, 40), (9, 36, 5, 3, 18, None), (130, 128, 16, 1, 64, 128), (5, 48, 2, 2, 20, 12), (300, 64, 4, 2, 72, 8)])
+def test_routed_experts_whose_weights_multiply_their_inputs(dtype, n, hidden, experts, top, inner, shared):
+    from yalis_b200.config.spec import PartSpec
+    from yalis_b200.parts.base import make_part
+    t = ff_tensors(hidden, experts, inner, shared, seed=n, dtype=dtype)
+    part = make_part("feed_forward", PartSpec("routed_experts", {
+        "hidden_size": hidden, "experts": experts, "top": top, "expert_size": inner, "activation": "silu", "gated": True,
+        "score": "sigmoid", "renorm": False, "weight_on": "input", "shared_size": shared, "shared_gate": shared is not None}))
+    local = {"router": t["router"]}
+    for e in range(experts):
+        local.update({f"expert_{e}_{p}": t[f"e{e}.{p}"] for p in ("gate", "up", "down")})
+    if shared:
+        local.update({"shared_gate_proj": t["shared.gate"], "shared_up": t["shared.up"], "shared_down": t["shared.down"],
+                      "shared_gate": t["shared.sg"]})
+    assert set(local) == set(part.param_specs())
+    part.load({k: (v if k in ("router", "shared_gate") else v.to(dtype)).to(DEV) for k, v in local.items()})
+    g = torch.Generator().manual_seed(7)
+    x = torch.randn(n, hidden, generator=g).to(dtype)
+
+    class Ctx:
+        req_of_token = i32([0] * n)
+    got = part.forward(x.to(DEV), Ctx).double().cpu()
+    want = plain.moe_ff(x.double(), {k: v.double() for k, v in t.items()},
+                        "", {"router": {"top": top}, "shared": {"ff": shared} if shared else None})
+    if dtype == torch.float32:
+        torch.testing.assert_close(got, want, rtol=1e-4, atol=1e-4)
+    else:       # a token whose best scores are nearly equal may run another expert than the float64 model
+        err = (got - want).abs().max(dim=1).values / want.abs().max()
+        assert float((err > 4e-2).float().mean()) <= 0.06
+    # a weight on the input is not a weight on the output: the same part with the weight behind the expert differs
+    other = make_part("feed_forward", PartSpec("routed_experts", {**part.spec.params, "weight_on": "output"}))
+    other.load({k: (v if k in ("router", "shared_gate") else v.to(dtype)).to(DEV) for k, v in local.items()})
+    if dtype == torch.float32:
+        assert float((other.forward(x.to(DEV), Ctx).double().cpu() - want).abs().max()) > 1e-2
+
+
+# ---- whole models ------------------------------------------------------------------------------------------------------
+
+TOL = {"float32": 2e-4, "bfloat16": 6e-2}
+LENGTHS = {"A": [1, 5, 33, 70, 21, 48], "B": [2, 40, 9, 64, 17, 90], "C": [3, 37, 18, 130, 12, 66], "D": [7, 1, 50, 19, 33, 4]}
+PAGE = {"A": 16, "B": 8, "C": 64, "D": 16}
+_oracle = {}
+
+
+def requests_for(which):
+    cfg, _ = plain.read_folder(sazavik_dir(which))
+    g = torch.Generator().manual_seed(ord(which))
+    return {f"r{i}": torch.randint(0, cfg["vocab"], (n,), generator=g).tolist() for i, n in enumerate(LENGTHS[which])}
+
+
+def oracle(which):
+    if which not in _oracle:
+        cfg, w = plain.read_folder(sazavik_dir(which))
+        _oracle[which] = {rid: plain.forward(cfg, w, t).numpy() for rid, t in requests_for(which).items()}
+    return _oracle[which]
+
+
+def replay(which, dtype, steps, max_tokens, graphs=False):
+    from yalis_b200.engine.replay import Replayer
+    rep = Replayer(sazavik_dir(which), dtype, max_tokens, page_size=PAGE[which], graphs=graphs)
+    out = {}
+    for s in steps:
+        r = rep.run_step(s)
+        if r is not None:
+            out[s["step"]] = r
+    rep.engine.manager.check()
+    for grp in rep.engine.groups:
+        assert rep.engine.manager.free_pages(grp.name) == grp.num_pages          # every page came back
+    return out, rep
+
+
+def compare(got, want, tol, what, outliers=0.0):
+    assert set(got) == set(want), what
+    total = bad = 0
+    for rid in want:
+        assert got[rid].shape == want[rid].shape, (what, rid)
+        scale = np.abs(want[rid]).max()
+        err = np.abs(got[rid] - want[rid]).max(axis=1) / scale
+        total += len(err)
+        bad += int((err > tol).sum())
+        if err.max() > tol and not outliers:
+            raise AssertionError(f"{what}: request {rid} differs by {err.max():.3e} (tolerance {tol}); first wrong "
+                                 f"position {int(np.argmax(err > tol))} of {len(err)}")
+    assert bad <= outliers * total, f"{what}: {bad} of {total} positions differ by more than {tol}"
+
+
+@pytest.mark.parametrize("which", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_requests_cut_four_ways_agree_with_the_plain_model(which, dtype):
+    reqs, want = requests_for(which), oracle(which)
+    vocab = plain.read_folder(sazavik_dir(which))[0]["vocab"]
+    results = {}
+    # bfloat16: a token whose two best router scores are nearly equal may run another expert than the float64 model
+    outliers = 0.0 if dtype == "float32" else 0.08
+    for name, steps in (("whole", traces.whole(reqs)), ("tail", traces.tail_decoded(reqs, tail=12)),
+                        ("portions", traces.portions(reqs, seed=3)), ("mixed", traces.mixed(reqs, seed=5, tail=6))):
+        steps = traces.number(steps)
+        out, rep = replay(which, dtype, steps, traces.peak_tokens(steps, max(64, PAGE[which])))
+        got = traces.collect(steps, out, vocab)
+        compare(got, want, TOL[dtype], f"{which} {dtype} {name}", outliers=outliers)
+        results[name] = got
+    # how a request was cut, what ran beside it and which pages and slots it had leave (nearly) no trace
+    for name in ("tail", "portions", "mixed"):
+        for rid in want:
+            scale = np.abs(want[rid]).max()
+            diff = np.abs(results[name][rid] - results["whole"][rid]).max(axis=1) / scale
+            if dtype == "float32":
+                assert diff.max() < 2e-5, (name, rid)
+            else:
+                assert np.mean(diff > 6e-2) <= outliers, (name, rid)
+
+
+@pytest.mark.parametrize("which", ["A", "C"])
+def test_steps_replayed_from_recordings_give_the_same(which):
+    """Decoded tokens through recorded steps (CUDA graphs): the routing is decided on the device every time."""
+    reqs, want = requests_for(which), oracle(which)
+    vocab = plain.read_folder(sazavik_dir(which))[0]["vocab"]
+    steps = traces.number(traces.tail_decoded(reqs, tail=12))
+    launched, _ = replay(which, "float32", steps, traces.peak_tokens(steps, max(64, PAGE[which])))
+    recorded, rep = replay(which, "float32", steps, traces.peak_tokens(steps, max(64, PAGE[which])), graphs=True)
+    assert rep.steps_replayed > 40
+    a, b = traces.collect(steps, launched, vocab), traces.collect(steps, recorded, vocab)
+    compare(b, want, TOL["float32"], f"{which} recorded")
+    for rid in a:
+        assert np.abs(a[rid] - b[rid]).max() / np.abs(a[rid]).max() < 1e-6
+
+
+@pytest.mark.parametrize("which", ["A", "C"])
+def test_the_residual_stream_after_every_layer(which):
+    from yalis_b200.engine.engine import Engine, StepEntry
+    d = sazavik_dir(which)
+    cfg, w = plain.read_folder(d)
+    tokens = requests_for(which)["r2"]
+    want = []
+    plain.forward(cfg, w, tokens, taps=want)
+    eng = Engine(d, dtype="float32", page_size=16, num_pages=8, max_slots=2, max_context=128)
+    eng.add_request("x")
+    seen = []
+    inner = eng.model.forward
+    eng.model.forward = lambda ctx, caches: inner(ctx, caches, tap=lambda i, x: seen.append(x.double().cpu()))
+    eng.run([StepEntry("x", tokens, [len(tokens) - 1])])
+    assert len(seen) == len(want) == 5
+    for i, (a, b) in enumerate(zip(seen, want)):
+        assert float((a - b).abs().max() / b.abs().max()) < 2e-5, f"layer {i}"
+
+
+@pytest.mark.parametrize("which, dtype", [("A", "float32"), ("B", "float32"), ("C", "bfloat16")])
+def test_long_decoding_keeps_to_the_plain_model(which, dtype):
+    """300 tokens one by one after a two-token prompt: every window and chunk border passes over decoded tokens many
+    times, and the pages behind them are given back and used again (the pool is far smaller than the sequence)."""
+    from yalis_b200.engine.engine import Engine, StepEntry
+    d = sazavik_dir(which)
+    cfg, w = plain.read_folder(d)
+    g = torch.Generator().manual_seed(9)
+    tokens = torch.randint(0, cfg["vocab"], (302,), generator=g).tolist()
+    want = plain.forward(cfg, w, tokens).numpy()
+    eng = Engine(d, dtype=dtype, page_size=8, num_pages=14, max_slots=2, max_context=384)
+    eng.add_request("x")
+    rows = [eng.run([StepEntry("x", tokens[:2], [0, 1])]).logits.cpu().numpy()]
+    for t in tokens[2:]:
+        rows.append(eng.run([StepEntry("x", [t], [0])]).logits.cpu().numpy())
+    got = np.concatenate(rows)
+    eng.check_device_errors()
+    err = np.abs(got - want).max(axis=1) / np.abs(want).max()
+    if dtype == "float32":
+        assert err.max() < 2e-4
+    else:
+        assert np.mean(err > 6e-2) < 0.08
+
+
+def test_a_slot_and_its_pages_used_again_start_clean():
+    from yalis_b200.engine.engine import Engine, StepEntry
+    d = sazavik_dir("C")
+    reqs = requests_for("C")
+    eng = Engine(d, dtype="float32", page_size=64, num_pages=3, max_slots=1, max_context=192)
+    first = None
+    for rid in ("r3", "r1", "r3"):
+        assert eng.add_request(rid) == 0                       # the only slot, every time
+        out = eng.run([StepEntry(rid, reqs[rid], [len(reqs[rid]) - 1])]).logits.cpu().numpy()
+        eng.finish_request(rid)
+        if rid == "r3":
+            if first is None:
+                first = out
+            else:
+                assert np.array_equal(first, out)              # what r1 left in slot and pages does not show
+
+
+@pytest.mark.parametrize("which", ["A", "B"])
+def test_greedy_generation_through_the_entry_point(which):
+    from yalis_b200 import InferenceConfig, LLMEngine, ModelConfig
+    d = sazavik_dir(which)
+    cfg, w = plain.read_folder(d)
+    g = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(0, cfg["vocab"], (n,), generator=g).tolist() for n in (3, 19, 40, 7, 26)]
+    engine = LLMEngine(ModelConfig(model_name=f"sazavik-tiny-{which}", model_path=d, precision="fp32"),
+                       InferenceConfig(max_batch_size=3, max_length_of_generated_sequences=64, temperature=0.0, top_p=0.0,
+                                       page_size=PAGE[which]))
+    tokens, metrics = engine.generate(prompts, tokens_to_generate=10)[:2]
+    for p, row in zip(prompts, tokens.cpu().tolist()):
+        assert row == plain.greedy(cfg, w, p, 10)
+
+
+def test_the_replay_program_runs_a_sazavik_folder(tmp_path):
+    reqs = {k: v for k, v in requests_for("B").items() if k in ("r1", "r2")}
+    steps = traces.number(traces.portions(reqs, seed=1))
+    out_dir = tmp_path / "out"
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", sazavik_dir("B"), "--dtype", "float32",
+                           "--out", str(out_dir), "--max-tokens", str(traces.peak_tokens(steps))],
+                          input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [l for l in proc.stdout.splitlines() if l.startswith("done")] == [f"done {s['step']}" for s in steps]
+    vocab = plain.read_folder(sazavik_dir("B"))[0]["vocab"]
+    outputs = {s["step"]: np.fromfile(out_dir / f"{s['step']}.f32", dtype="<f4") for s in steps}
+    compare(traces.collect(steps, outputs, vocab), {k: oracle("B")[k] for k in reqs}, TOL["float32"], "program")

@@ -285,6 +285,83 @@ PRESETS["pametar-1b"] = _pametar_stack(2048, 32000, 8, 4, 16, 128, 256, 768, 64,
 PRESETS["pametar-3b"] = _pametar_stack(3072, 32000, 12, 4, 24, 128, 384, 1024, 64, 24, 128, 32, 4, 1024)
 
 
+# ---- Sazavik -------------------------------------------------------------------------------------------------------
+
+def _sz_mixer(kind, heads, kv_heads, dim, vdim, size, scale, rot=None, q_temp=None, kv_from=None):
+    mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "mask": {"size": size}, "scale": scale}
+    if rot is not None:
+        mixer["rot"] = {"dims": rot[0], "base": rot[1]}
+    if q_temp is not None:
+        mixer["q_temp"] = {"coef": q_temp[0], "every": q_temp[1]}
+    if kv_from is not None:
+        mixer["kv_from"] = kv_from
+    return {"type": kind, "mixer": mixer}
+
+
+def _sz_dense(ff, limit):
+    return {"kind": "dense", "ff": ff, "limit": limit}
+
+
+def _sz_layer(mixer, mlp):
+    return {**mixer, "mlp": mlp}
+
+
+def _sazavik(width, vocab, layers, softcap=30.0, eps=1e-5) -> Dict[str, Any]:
+    cfg = {"architecture": "Sazavik", "width": width, "vocab": vocab, "norm": {"eps": eps}, "layers": layers}
+    if softcap is not None:
+        cfg["logit_softcap"] = softcap
+    return cfg
+
+
+def _sazavik_stack(width, vocab, groups, heads, kv_heads, dim, chunk, window, ff, experts, top, expert_ff, shared) -> Dict[str, Any]:
+    """``groups`` times (half-split chunked attention + dense, windowed attention with distance bias + experts,
+    interleaved chunked attention with sink and gate + dense, a reader of the windowed layer's keys + experts)."""
+    layers = []
+    for _ in range(groups):
+        at = len(layers)
+        moe = _moe(experts, top, expert_ff, shared)
+        layers.append(_sz_layer(_sz_mixer("attention_2", heads, kv_heads, dim, dim, chunk, dim ** -0.5, rot=(dim // 2, 10000.0)),
+                                _sz_dense(ff, 7.0)))
+        layers.append(_sz_layer(_sz_mixer("attention_3", heads, kv_heads, dim, dim, window, dim ** -0.5, q_temp=(0.1, 1024)), moe))
+        layers.append(_sz_layer(_sz_mixer("attention", heads, kv_heads, dim, dim, chunk, dim ** -0.5, rot=(dim, 500000.0)),
+                                _sz_dense(ff, 7.0)))
+        layers.append(_sz_layer(_sz_mixer("attention_3", heads, kv_heads, dim, dim, window, dim ** -0.5, q_temp=(0.1, 1024),
+                                          kv_from=at + 1), moe))
+    return _sazavik(width, vocab, layers)
+
+
+# Test shapes.  A: all three mixers, a reader with a wider window than the layer whose keys it reads, a layer without
+# feed-forward, an expert layer without a shared expert, chunks and windows that are multiples of nothing.  B: sizes
+# that are multiples of nothing (no row on a 16-byte boundary), one key head, all heads turning whole, three of five
+# experts, no soft cap.  C: the head sizes of the tensor-core kernels, a window of one position, a chunk of a page,
+# sixteen experts, a query temperature that changes every few positions.  D: every expert chosen, masks that never
+# bind, as many key heads as heads, key and value sizes apart.
+PRESETS["sazavik-tiny-A"] = _sazavik(64, 96, [
+    _sz_layer(_sz_mixer("attention_3", 4, 2, 12, 20, 9, 0.3, q_temp=(0.4, 5)), _moe(6, 2, 16, 24)),
+    _sz_layer(_sz_mixer("attention", 4, 2, 16, 16, 11, 0.25, rot=(8, 100.0)), _sz_dense(40, 1.5)),
+    _sz_layer(_sz_mixer("attention_3", 4, 2, 12, 20, 23, 0.3, q_temp=(0.7, 3), kv_from=0), None),
+    _sz_layer(_sz_mixer("attention_2", 2, 1, 24, 8, 13, 0.2, rot=(10, 50.0)), _moe(4, 1, 24, None)),
+    _sz_layer(_sz_mixer("attention", 3, 3, 10, 14, 7, 0.35, rot=(10, 30.0)), _sz_dense(24, 0.8))], softcap=12.0)
+PRESETS["sazavik-tiny-B"] = _sazavik(36, 50, [
+    _sz_layer(_sz_mixer("attention_2", 3, 1, 10, 6, 5, 0.3, rot=(10, 20.0)), _moe(5, 3, 18, 14)),
+    _sz_layer(_sz_mixer("attention_3", 3, 3, 6, 10, 4, 0.4, q_temp=(1.5, 2)), _sz_dense(30, 3.0)),
+    _sz_layer(_sz_mixer("attention", 2, 1, 14, 5, 3, 0.35, rot=(2, 7.0)), _moe(3, 2, 10, 6))], softcap=None, eps=1e-6)
+PRESETS["sazavik-tiny-C"] = _sazavik(128, 160, [
+    _sz_layer(_sz_mixer("attention", 4, 2, 64, 64, 16, 0.125, rot=(32, 10000.0)), _moe(16, 4, 32, 64)),
+    _sz_layer(_sz_mixer("attention_3", 4, 4, 32, 32, 1, 0.18, q_temp=(0.3, 7)), _sz_dense(256, 2.5)),
+    _sz_layer(_sz_mixer("attention_2", 8, 2, 16, 16, 40, 0.25, rot=(16, 1000.0)), _moe(8, 2, 64, None)),
+    _sz_layer(_sz_mixer("attention_3", 2, 1, 128, 128, 50, 0.09, q_temp=(0.2, 16)), _sz_dense(128, 1.0)),
+    _sz_layer(_sz_mixer("attention_3", 2, 1, 128, 128, 33, 0.09, q_temp=(0.6, 4), kv_from=3), _moe(16, 4, 32, 64))], softcap=20.0)
+PRESETS["sazavik-tiny-D"] = _sazavik(48, 64, [
+    _sz_layer(_sz_mixer("attention_2", 2, 2, 8, 24, 4096, 0.3, rot=(4, 9.0)), _moe(2, 2, 20, 12)),
+    _sz_layer(_sz_mixer("attention", 2, 2, 16, 8, 4096, 0.25, rot=(16, 7.0)), _sz_dense(36, 50.0)),
+    _sz_layer(_sz_mixer("attention_3", 4, 4, 8, 8, 4096, 0.3, q_temp=(0.5, 4096)), _moe(2, 2, 20, 12))], softcap=40.0)
+# Sizes that resemble a real model's layers (random weights, for the benchmark): the widths, head and expert counts of
+# the Vepivik benchmark models, so that the two designs stand beside each other at equal size.
+PRESETS["sazavik-1b"] = _sazavik_stack(2048, 32000, 4, 16, 8, 128, 2048, 1024, 4096, 16, 2, 1408, 2048)
+PRESETS["sazavik-3b"] = _sazavik_stack(3072, 32000, 6, 24, 8, 128, 2048, 1024, 6144, 32, 4, 1024, 3072)
+
+
 def preset(name: str) -> Dict[str, Any]:
     """A fresh copy of the named configuration dictionary."""
     for key in (name, name.split("/")[-1], name.split("/")[-1].replace("Meta-", "")):

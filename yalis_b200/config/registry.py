@@ -87,4 +87,4 @@ def load_config(model_dir: str):
 
 def _ensure_builtin() -> None:
     # Importing the module registers the architecture it defines.
-    from yalis_b200.models import llama, pametar, tirezen, vepivik  # noqa: F401
+    from yalis_b200.models import llama, pametar, sazavik, tirezen, vepivik  # noqa: F401

@@ -103,6 +103,10 @@ class ModelSpec:
     # the residual stream is kept in this many copies, all equal to the entering rows at the start; the layers'
     # blocks and the final norm must be kinds that read and write such a stream (None: the plain stream [N, hidden])
     stream_copies: Optional[int] = None
+    # a part of category ``norm`` applied to the token rows as they enter the stream (float32, after the embedding
+    # scale and before the entry part), with "<param>" -> tensor name (None: the rows enter as they are)
+    embedding_norm: Optional[PartSpec] = None
+    embedding_norm_names: Mapping[str, str] = field(default_factory=dict)
 
     def __post_init__(self):
         for i, e in enumerate(self.schedule):

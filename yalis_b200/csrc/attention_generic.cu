@@ -8,8 +8,12 @@
 // path and the twin against which the faster bfloat16 kernels are tested.
 //
 //   S = (q . k_j) * scale for keys j with  pos - window < j <= pos   (window 0: all j <= pos)
+//   with chunk C > 0 also  j >= floor(pos / C) * C      (position 0 starts the first chunk)
+//   S <- S - slope_h * (pos - j)                                        (slopes given only)
 //   S <- cap * tanh(S / cap)                                            (cap > 0 only)
-//   O = softmax(S) V, or with a sink: exp(S_j) / (1 + sum_i exp(S_i)) V  (a key of score 0 and no value)
+//   O = softmax(S) V, or with a sink: exp(S_j) / (exp(z_h) + sum_i exp(S_i)) V  (a key of score z_h and no value;
+//   z_h = sink_logits[h], or 0 without that array)
+//   O <- O * sigmoid(gate[t, h, :])                                     (gate given only)
 // Values may have a head size of their own (hsv).
 // Mask by absolute position: yalis/attention/backend_impl/sdpa_and_flex.py:15-19, 301-307.
 // KV head of query head h: h / (nh / g)                                 (:59-67).
@@ -28,7 +32,9 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, int q_st
                                                const int32_t* __restrict__ block_table, int table_width,
                                                int page_size, int num_pages, int nh, int g, int hs, int hsv,
                                                float scale, int window, float softcap, int sink,
-                                               float out_scale) {
+                                               float out_scale, int chunk, const float* __restrict__ sink_logits,
+                                               const float* __restrict__ slopes, const T* __restrict__ gate,
+                                               int gate_stride) {
   extern __shared__ float smem[];  // [kWarps][hsv] accumulators, then m[kWarps], l[kWarps]
   pdl_launch_dependents();
   pdl_wait();
@@ -49,7 +55,9 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, int q_st
     acc[i] = 0.f;
   }
   float m = -INFINITY, l = 0.f;
-  const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  if (chunk > 0) lo = max(lo, (pos / chunk) * chunk);
+  const float slope = slopes ? slopes[h] : 0.f;
   const int32_t* bt = block_table + (size_t)req * table_width;
   for (int j = lo + warp; j <= pos; j += kWarps) {
     const int pi = j / page_size;
@@ -65,6 +73,7 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, int q_st
       if (i < per_lane && d < hs) dot += qr[i] * to_f32<T>(kp[d]);
     }
     float s = warp_sum(dot) * scale;
+    if (slopes) s -= slope * (float)(pos - j);
     if (softcap > 0.f) s = softcap * tanhf(s / softcap);
     const float m_new = fmaxf(m, s);
     const float corr = expf(m - m_new);
@@ -93,8 +102,9 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, int q_st
   float mm = -INFINITY;
 #pragma unroll
   for (int w = 0; w < kWarps; ++w) mm = fmaxf(mm, m_s[w]);
-  if (sink) mm = fmaxf(mm, 0.f);
-  float ll = sink ? expf(-mm) : 0.f;
+  const float sink_z = (sink && sink_logits) ? sink_logits[h] : 0.f;
+  if (sink) mm = fmaxf(mm, sink_z);
+  float ll = sink ? expf(sink_z - mm) : 0.f;
   float wgt[kWarps];
 #pragma unroll
   for (int w = 0; w < kWarps; ++w) {
@@ -106,7 +116,9 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, int q_st
     float o = 0.f;
 #pragma unroll
     for (int w = 0; w < kWarps; ++w) o += acc_s[w * hsv + d] * wgt[w];
-    op[d] = from_f32<T>(ll > 0.f ? o / ll * out_scale : 0.f);
+    float res = ll > 0.f ? o / ll * out_scale : 0.f;
+    if (gate) res *= 1.0f / (1.0f + expf(-to_f32<T>(gate[(size_t)t * gate_stride + (size_t)h * hsv + d])));
+    op[d] = from_f32<T>(res);
   }
 }
 
@@ -118,7 +130,8 @@ YALIS_API int yalis_paged_attention_generic(const void* q, int q_stride, void* o
                                             const int32_t* block_table, int table_width, int page_size,
                                             int num_pages, int n_tokens, int nh, int g, int hs, int hsv,
                                             float scale, int window, float softcap, int sink, float out_scale,
-                                            cudaStream_t stream) {
+                                            int chunk, const float* sink_logits, const float* slopes, const void* gate,
+                                            int gate_stride, cudaStream_t stream) {
   if (n_tokens <= 0) return YALIS_OK;
   if (hs <= 0 || hs > 32 * kMaxPerLane || hsv <= 0 || hsv > 32 * kMaxPerLane || g <= 0 || nh % g != 0 || nh > 65535)
     return YALIS_ERR_SHAPE;
@@ -128,6 +141,7 @@ YALIS_API int yalis_paged_attention_generic(const void* q, int q_stride, void* o
                        return yalis_launch(paged_attention_generic_kernel<T>, grid, dim3(kWarps * 32), smem, stream,
                                            (const T*)q, q_stride, (T*)out, out_stride, (const T*)k_pool,
                                            (const T*)v_pool, positions, req_of_token, block_table, table_width,
-                                           page_size, num_pages, nh, g, hs, hsv, scale, window, softcap, sink, out_scale));
+                                           page_size, num_pages, nh, g, hs, hsv, scale, window, softcap, sink, out_scale, chunk,
+                                           sink_logits, slopes, (const T*)gate, gate_stride));
   return YALIS_OK;
 }

@@ -28,7 +28,9 @@
 //
 // The general form (GEN) adds what some mixers ask of attention: scores squeezed by
 // c * tanh(s / c), a sink (a key of score 0 and no value: 1 more in the denominator), a
-// factor on the result, and weights that meet V with 16 bits of mantissa instead of 8:
+// learned score of that sink per head, a chunked mask (a row sees only the keys of its own chunk of C positions),
+// a distance bias slope_h * (pos - key) taken off the score, a sigmoid gate on the result,
+// a factor on the result, and weights that meet V with 16 bits of mantissa instead of 8:
 // P is split into its bfloat16 rounding and the bfloat16 rounding of the rest, and both
 // halves go through the tensor cores (the sum of the weights is float32 in either form).
 #include "common.cuh"
@@ -59,6 +61,11 @@ struct AttnParams {
   float out_scale;             // GEN: factor on the result
   int exact_weights;           // ask for the general form even without cap, sink or factor
   int window;                  // 0: none
+  int chunk;                   // GEN: C > 0: a row at position p sees keys >= floor(p / C) * C only
+  const float* sink_logits;    // GEN: [nh] score of the sink per head (null: 0)
+  const float* slopes;         // GEN: [nh] slope_h * (p - key) is taken off the score (null: none)
+  const __nv_bfloat16* gate;   // GEN: [N, gate_stride] the result is multiplied by sigmoid(gate[t, head, :]) (null: not)
+  int gate_stride;
   int n_splits;
   float* part_o;               // [N, nh, n_splits, HS] (split mode)
   float* part_ml;              // [N, nh, n_splits, 2]
@@ -137,24 +144,41 @@ __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* k_dst, __nv_bfloat16
 
 // DEC: the block has at most 16 rows; warps split the keys of a tile instead of the rows.
 // A score in the exp2 domain: s * scale * log2(e), or with a cap c: c * tanh(s * scale / c) * log2(e).
+// `bias_log2`: what is taken off the scaled score before the cap, in the exp2 domain (the distance bias).
 template <bool GEN>
-__device__ __forceinline__ float score_log2(const AttnParams& p, float s) {
+__device__ __forceinline__ float score_log2(const AttnParams& p, float s, float bias_log2 = 0.f) {
   if (GEN && p.cap_log2 > 0.f) {
     // tanh(x) = 1 - 2 / (exp(2x) + 1) with the fast exponential and reciprocal: absolute error about 3e-7, which
     // the cap multiplies to 1e-5 of a score at most (the float32 path uses tanhf in the exact kernel)
-    const float x = fminf(s * p.scale_over_cap, 15.f);
+    const float x = fminf(s * p.scale_over_cap - bias_log2 / p.cap_log2, 15.f);
     return p.cap_log2 * (1.0f - __fdividef(2.0f, __expf(2.0f * x) + 1.0f));
   }
-  return s * p.scale_log2;
+  return GEN ? s * p.scale_log2 - bias_log2 : s * p.scale_log2;
+}
+
+// The sink's score of a head in the exp2 domain.
+__device__ __forceinline__ float sink_log2(const AttnParams& p, int head) {
+  return p.sink_logits ? p.sink_logits[head] * 1.4426950408889634f : 0.f;
+}
+// sigmoid of the gate that belongs to out[tok, head, d].
+__device__ __forceinline__ float gate_factor(const AttnParams& p, int tok, int head, int hs, int d) {
+  return 1.0f / (1.0f + __expf(-__bfloat162float(p.gate[(size_t)tok * p.gate_stride + (size_t)head * hs + d])));
+}
+// The first key a row at position `pos` sees.
+template <bool GEN>
+__device__ __forceinline__ int first_visible(const AttnParams& p, int pos) {
+  int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+  if (GEN && p.chunk > 0) lo = max(lo, (pos / p.chunk) * p.chunk);
+  return lo;
 }
 
 // Normalisation of a finished row: with a sink the denominator gains exp2(0 - m) for the row's maximum m
 // (the maximum itself is raised to 0 first when all scores lie below it).
 template <bool GEN>
-__device__ __forceinline__ float finish_factor(const AttnParams& p, float m, float l) {
+__device__ __forceinline__ float finish_factor(const AttnParams& p, float m, float l, float sink_z = 0.f) {
   if (GEN && p.sink) {
-    // numerator and denominator are relative to exp2(m): the sink is exp2(-m) in that unit
-    l += exp2f(-m);
+    // numerator and denominator are relative to exp2(m): the sink is exp2(z - m) in that unit
+    l += exp2f(sink_z - m);
     return p.out_scale / l;
   }
   return l > 0.f ? (GEN ? p.out_scale : 1.0f) / l : 0.f;
@@ -194,7 +218,8 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_mma_kernel(const 
   const int last_tok = last_row / p.per;
   const int pos_first = p.positions[tok0 + first_tok];
   const int pos_last = p.positions[tok0 + last_tok];
-  const int lo_key = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
+  const int lo_key = first_visible<GEN>(p, pos_first);      // positions grow along a portion: the smallest bound
+  const int lo_last = first_visible<GEN>(p, pos_last);      // and the largest
   const int hi_key = pos_last;
   int tile_lo = lo_key / BN, tile_hi = hi_key / BN + 1;     // key tiles [tile_lo, tile_hi)
   if (p.n_splits > 1) {
@@ -238,13 +263,16 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_mma_kernel(const 
     ldmatrix_x4(qf[ks], q_s + r * LD + c);
   }
   // Rows of this thread: gid and gid + 8 of the warp's 16.
-  int row_pos[2];
+  int row_pos[2], row_lo[2];
   bool row_ok[2];
+  float row_slope[2] = {0.f, 0.f};      // in the exp2 domain
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     const int row = row0 + wrow + gid + i * 8;
     row_ok[i] = row < n_rows;
     row_pos[i] = row_ok[i] ? p.positions[tok0 + row / p.per] : -1;
+    row_lo[i] = row_ok[i] ? first_visible<GEN>(p, row_pos[i]) : 0;
+    if (GEN && p.slopes && row_ok[i]) row_slope[i] = p.slopes[kvh * p.per + row % p.per] * 1.4426950408889634f;
   }
 
   float o[DT][4];
@@ -283,8 +311,7 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_mma_kernel(const 
     // ---- mask, online softmax (exp2 domain) -----------------------------------------
     float m_new[2] = {m_run[0], m_run[1]};
     // A tile strictly inside every row's visible range needs no mask (the common case in decode).
-    const bool inner = key0 + BN - 1 <= pos_first && (p.window <= 0 || key0 > pos_last - p.window) &&
-                       row0 + RB <= n_rows;
+    const bool inner = key0 + BN - 1 <= pos_first && key0 >= lo_last && row0 + RB <= n_rows && !(GEN && p.slopes);
     if (inner) {
 #pragma unroll
       for (int j = 0; j < ST; ++j) {
@@ -301,8 +328,8 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_mma_kernel(const 
         for (int e = 0; e < 4; ++e) {
           const int i = e >> 1;
           const int key = key0 + wkey + j * 8 + tig * 2 + (e & 1);
-          const bool vis = row_ok[i] && key <= row_pos[i] && (p.window <= 0 || key > row_pos[i] - p.window);
-          const float v = vis ? score_log2<GEN>(p, s[j][e]) : -INFINITY;
+          const bool vis = row_ok[i] && key <= row_pos[i] && key >= row_lo[i];
+          const float v = vis ? score_log2<GEN>(p, s[j][e], row_slope[i] * (float)(row_pos[i] - key)) : -INFINITY;
           s[j][e] = v;
           m_new[i] = fmaxf(m_new[i], v);
         }
@@ -441,13 +468,17 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_mma_kernel(const 
       const int t = row / p.per, h = row - t * p.per;
       const int tok = tok0 + t, head = kvh * p.per + h;
       if (p.n_splits == 1) {
+        float sz = 0.f;
         if (GEN && p.sink) {
-          const float up = fmaxf(mm, 0.f);          // the sink may be the row's largest score
+          sz = sink_log2(p, head);
+          const float up = fmaxf(mm, sz);           // the sink may be the row's largest score
           acc *= exp2f(mm - up);
           ll = ll * exp2f(mm - up);
           mm = up;
         }
-        p.out[(size_t)tok * p.out_stride + (size_t)head * HS + d] = __float2bfloat16_rn(acc * finish_factor<GEN>(p, mm, ll));
+        float res = acc * finish_factor<GEN>(p, mm, ll, sz);
+        if (GEN && p.gate) res *= gate_factor(p, tok, head, HS, d);
+        p.out[(size_t)tok * p.out_stride + (size_t)head * HS + d] = __float2bfloat16_rn(res);
       } else {
         const size_t slot = ((size_t)tok * p.nh + head) * p.n_splits + split;
         p.part_o[slot * HS + d] = acc;
@@ -483,13 +514,17 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_mma_kernel(const 
             ll += ml[(base + sp) * 2 + 1] * f;
             acc += po[(base + sp) * HS + d] * f;
           }
+          float sz = 0.f;
           if (GEN && p.sink) {
-            const float up = fmaxf(mm, 0.f);
+            sz = sink_log2(p, head);
+            const float up = fmaxf(mm, sz);
             acc *= exp2f(mm - up);
             ll = ll * exp2f(mm - up);
             mm = up;
           }
-          p.out[(size_t)tok * p.out_stride + (size_t)head * HS + d] = __float2bfloat16_rn(acc * finish_factor<GEN>(p, mm, ll));
+          float res = acc * finish_factor<GEN>(p, mm, ll, sz);
+          if (GEN && p.gate) res *= gate_factor(p, tok, head, HS, d);
+          p.out[(size_t)tok * p.out_stride + (size_t)head * HS + d] = __float2bfloat16_rn(res);
         }
         if (threadIdx.x == 0) p.tickets[blockIdx.y] = 0;
       }
@@ -503,17 +538,22 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_mma_kernel(const 
     const int tok = tok0 + t, head = kvh * p.per + h;
     float inv;
     if (GEN && p.sink) {
-      const float up = fmaxf(m_run[i], 0.f);
+      const float sz = sink_log2(p, head);
+      const float up = fmaxf(m_run[i], sz);
       const float down = exp2f(m_run[i] - up);       // m_run = -inf (no visible key) gives 0
-      inv = down * finish_factor<GEN>(p, up, l_run[i] * down);
+      inv = down * finish_factor<GEN>(p, up, l_run[i] * down, sz);
     } else {
       inv = finish_factor<GEN>(p, m_run[i], l_run[i]);
     }
     __nv_bfloat16* dst = p.out + (size_t)tok * p.out_stride + (size_t)head * HS;
 #pragma unroll
     for (int d = 0; d < DT; ++d) {
-      __nv_bfloat162 v = __floats2bfloat162_rn(o[d][i * 2] * inv, o[d][i * 2 + 1] * inv);
-      *reinterpret_cast<__nv_bfloat162*>(dst + d * 8 + tig * 2) = v;
+      float v0 = o[d][i * 2] * inv, v1 = o[d][i * 2 + 1] * inv;
+      if (GEN && p.gate) {
+        v0 *= gate_factor(p, tok, head, HS, d * 8 + tig * 2);
+        v1 *= gate_factor(p, tok, head, HS, d * 8 + tig * 2 + 1);
+      }
+      *reinterpret_cast<__nv_bfloat162*>(dst + d * 8 + tig * 2) = __floats2bfloat162_rn(v0, v1);
     }
   }
   }
@@ -538,7 +578,7 @@ int launch_mode(const AttnParams& p, int n_requests, int max_rows, cudaStream_t 
 
 template <int HS>
 int launch(const AttnParams& p, int n_requests, int max_rows, cudaStream_t stream) {
-  const bool general = p.cap_log2 > 0.f || p.sink || p.out_scale != 1.0f || p.exact_weights;
+  const bool general = p.cap_log2 > 0.f || p.sink || p.out_scale != 1.0f || p.exact_weights || p.chunk > 0 || p.slopes || p.gate;
   if (general)
     return max_rows <= 16 ? launch_mode<HS, true, true>(p, n_requests, max_rows, stream)
                           : launch_mode<HS, false, true>(p, n_requests, max_rows, stream);
@@ -571,7 +611,9 @@ YALIS_API int yalis_paged_attention_mma_general(const void* q, int q_stride, voi
                                                 int page_size, int num_pages, int n_tokens, int n_requests, int max_q_len,
                                                 int nh, int g, int hs, float scale, int window, int n_splits, float* scratch,
                                                 int32_t* tickets, float softcap, int sink, float out_scale,
-                                                int exact_weights, cudaStream_t stream) {
+                                                int exact_weights, int chunk, const float* sink_logits,
+                                                const float* slopes, const void* gate, int gate_stride,
+                                                cudaStream_t stream) {
   if (n_tokens <= 0 || n_requests <= 0) return YALIS_OK;
   if (softcap < 0.f) return YALIS_ERR_SHAPE;
   if (g <= 0 || nh % g != 0 || n_splits < 1 || max_q_len < 1) return YALIS_ERR_SHAPE;
@@ -592,6 +634,9 @@ YALIS_API int yalis_paged_attention_mma_general(const void* q, int q_stride, voi
   p.scale_over_cap = softcap > 0.f ? scale / softcap : 0.f;
   p.sink = sink; p.out_scale = out_scale; p.exact_weights = exact_weights;
   p.window = window; p.n_splits = n_splits;
+  p.chunk = chunk; p.sink_logits = sink ? sink_logits : nullptr; p.slopes = slopes;
+  p.gate = (const __nv_bfloat16*)gate; p.gate_stride = gate_stride;
+  if (chunk < 0) return YALIS_ERR_SHAPE;
   p.part_o = nullptr; p.part_ml = nullptr; p.tickets = tickets;
   if (n_splits > 1) {
     if (scratch == nullptr || tickets == nullptr || max_q_len * p.per > 16) return YALIS_ERR_SHAPE;
@@ -660,7 +705,8 @@ YALIS_API int yalis_paged_attention_mma(const void* q, int q_stride, void* out, 
                                         int32_t* tickets, cudaStream_t stream) {
   return yalis_paged_attention_mma_general(q, q_stride, out, out_stride, k_pool, v_pool, positions, q_start, req_of_token,
                                            block_table, table_width, page_size, num_pages, n_tokens, n_requests, max_q_len,
-                                           nh, g, hs, scale, window, n_splits, scratch, tickets, 0.f, 0, 1.0f, 0, stream);
+                                           nh, g, hs, scale, window, n_splits, scratch, tickets, 0.f, 0, 1.0f, 0, 0, nullptr, nullptr,
+                                           nullptr, 0, stream);
 }
 
 YALIS_API long long yalis_paged_attention_mma_noalloc_needed(int n_tokens, int n_requests, int nh, int g, int hs,

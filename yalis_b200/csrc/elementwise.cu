@@ -18,11 +18,14 @@ YALIS_API void yalis_set_pdl(int enabled) { g_pdl_enabled = enabled != 0; }
 // `scale` multiplies every value in float32 (1 for models that do not scale their embeddings).
 // With `from_slot`, a token whose entry there is not negative takes its id from chosen[from_slot[t]] instead of
 // ids[t]: the token that an earlier step chose for that request and left on the device.
+// With `norm_w` the row enters the stream normed: v / sqrt(mean(v^2) + norm_eps) * norm_w (float32, after `scale`).
 // --------------------------------------------------------------------------
 template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int32_t* __restrict__ ids,
                                  const int32_t* __restrict__ from_slot, const int32_t* __restrict__ chosen,
-                                 float* __restrict__ out, int width, int vocab, float scale, int32_t* bad_id) {
+                                 float* __restrict__ out, int width, int vocab, float scale, int32_t* bad_id,
+                                 const float* __restrict__ norm_w, float norm_eps) {
+  __shared__ float scratch[32];
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
@@ -38,6 +41,17 @@ __global__ void embedding_kernel(const T* __restrict__ table, const int32_t* __r
     return;
   }
   const T* row = table + (size_t)id * width;
+  if (norm_w != nullptr) {
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+      const float v = to_f32<T>(row[c]) * scale;
+      ss = __fmaf_rn(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)width + norm_eps);
+    for (int c = threadIdx.x; c < width; c += blockDim.x) o[c] = (to_f32<T>(row[c]) * scale * inv) * norm_w[c];
+    return;
+  }
   if (scale == 1.0f) {
     for (int c = threadIdx.x; c < width; c += blockDim.x) o[c] = to_f32<T>(row[c]);
   } else {
@@ -47,12 +61,12 @@ __global__ void embedding_kernel(const T* __restrict__ table, const int32_t* __r
 
 YALIS_API int yalis_embedding(const void* table, int dtype, const int32_t* ids, const int32_t* from_slot,
                               const int32_t* chosen, float* out, int n_tokens, int width, int vocab, float scale,
-                              int32_t* bad_id, cudaStream_t stream) {
+                              int32_t* bad_id, const float* norm_w, float norm_eps, cudaStream_t stream) {
   if (n_tokens <= 0) return YALIS_OK;
   if ((from_slot == nullptr) != (chosen == nullptr)) return YALIS_ERR_SHAPE;
   YALIS_DISPATCH_DTYPE(dtype, T,
                        return yalis_launch(embedding_kernel<T>, dim3(n_tokens), dim3(256), 0, stream, (const T*)table,
-                                           ids, from_slot, chosen, out, width, vocab, scale, bad_id));
+                                           ids, from_slot, chosen, out, width, vocab, scale, bad_id, norm_w, norm_eps));
   return YALIS_OK;
 }
 
@@ -301,6 +315,76 @@ YALIS_API int yalis_add_rmsnorm(float* x, const void* delta, int delta_dtype, in
       } else if (delta_dtype == YALIS_BF16) {
         return launch_add_rmsnorm<T, __nv_bfloat16>(x, delta, n_delta, (size_t)delta_stride, w, y, rows, n_out_rows,
                                                     width, eps, write_back, stream);
+      } else { return YALIS_ERR_DTYPE; });
+  return YALIS_OK;
+}
+
+// --------------------------------------------------------------------------
+// The same with a sub-layer's result that is itself normed (and may carry a bias) before it joins the stream:
+//   d = sum_s delta[s][r] (+ bias)                       float32
+//   d <- d * rsqrt(mean(d^2) + d_eps) * d_w             (only with d_w)
+//   h = x[r] + d;  x[r] = h (when write_back);  y[i] = (h * rsqrt(mean(h^2) + eps)) * w  (only with w)
+// One block per row; the row waits in shared memory between the passes, so every value is read once.
+// --------------------------------------------------------------------------
+template <typename T, typename TD>
+__global__ void __launch_bounds__(1024) add_normed_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ delta, int n_delta,
+                                                                  size_t delta_stride, const float* __restrict__ bias,
+                                                                  const float* __restrict__ d_w, float d_eps,
+                                                                  const float* __restrict__ w, T* __restrict__ y,
+                                                                  const int32_t* __restrict__ rows, int width, float eps,
+                                                                  int write_back) {
+  extern __shared__ float row_s[];        // [width]
+  __shared__ float scratch[32];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int i = blockIdx.x;
+  const int r = rows ? rows[i] : i;
+  if (r < 0) return;  // padded row
+  float* xr = x + (size_t)r * width;
+  const TD* dr = delta + (size_t)r * width;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    float d = sum_parts<TD>(dr + c, n_delta, delta_stride);
+    if (bias) d += bias[c];
+    row_s[c] = d;
+    ss = __fmaf_rn(d, d, ss);
+  }
+  float d_inv = 1.0f;
+  if (d_w) d_inv = rsqrtf(block_sum(ss, scratch) / (float)width + d_eps);
+  ss = 0.f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float d = d_w ? (row_s[c] * d_inv) * d_w[c] : row_s[c];
+    const float h = xr[c] + d;
+    if (write_back) xr[c] = h;
+    row_s[c] = h;
+    ss = __fmaf_rn(h, h, ss);
+  }
+  if (w == nullptr) return;
+  const float inv = rsqrtf(block_sum(ss, scratch) / (float)width + eps);
+  T* yr = y + (size_t)i * width;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) yr[c] = from_f32<T>((row_s[c] * inv) * w[c]);
+}
+
+// delta: [n_delta][rows_total][width] in delta_dtype; bias, d_w, w float32 [width] or null; y in out_dtype (unused
+// without w).
+YALIS_API int yalis_add_normed_rmsnorm(float* x, const void* delta, int delta_dtype, int n_delta, long long delta_stride,
+                                       const float* bias, const float* d_w, float d_eps, const float* w, void* y,
+                                       int out_dtype, const int32_t* rows, int n_out_rows, int width, float eps,
+                                       int write_back, cudaStream_t stream) {
+  if (n_out_rows <= 0) return YALIS_OK;
+  if (delta == nullptr || n_delta <= 0 || width <= 0 || width > 48 * 1024 / 4) return YALIS_ERR_SHAPE;
+  const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+  const size_t smem = (size_t)width * sizeof(float);
+  YALIS_DISPATCH_DTYPE(
+      out_dtype, T,
+      if (delta_dtype == YALIS_F32) {
+        return yalis_launch(add_normed_rmsnorm_kernel<T, float>, dim3(n_out_rows), dim3(threads), smem, stream, x,
+                            (const float*)delta, n_delta, (size_t)delta_stride, bias, d_w, d_eps, w, (T*)y, rows, width, eps,
+                            write_back);
+      } else if (delta_dtype == YALIS_BF16) {
+        return yalis_launch(add_normed_rmsnorm_kernel<T, __nv_bfloat16>, dim3(n_out_rows), dim3(threads), smem, stream, x,
+                            (const __nv_bfloat16*)delta, n_delta, (size_t)delta_stride, bias, d_w, d_eps, w, (T*)y, rows, width,
+                            eps, write_back);
       } else { return YALIS_ERR_DTYPE; });
   return YALIS_OK;
 }

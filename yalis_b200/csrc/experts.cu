@@ -21,10 +21,62 @@ namespace {
 constexpr int kMaxExperts = 1024;
 constexpr int kMaxTop = 32;
 
+// The choice of one token by one warp with scores sigmoid(logit): the `top` largest logits are chosen (the order of
+// the scores, without the ties that a saturated sigmoid would make; equal logits go to the smaller index), and the
+// weights are the chosen scores, divided by their sum + eps unless eps < 0, times `factor`.
+template <typename F>
+__device__ __forceinline__ void choose_experts_sigmoid(F logit, int E, int top, float eps, float factor, int lane,
+                                                       int32_t* __restrict__ ids, float* __restrict__ weights) {
+  constexpr int kPer = kMaxExperts / 32;
+  float s[kPer];
+#pragma unroll
+  for (int i = 0; i < kPer; ++i) s[i] = (lane + 32 * i) < E ? logit(lane + 32 * i) : -INFINITY;
+  float chosen_w = 0.f, total = 0.f;
+  int chosen_e = -1;
+  for (int j = 0; j < top; ++j) {
+    float best = -INFINITY;
+    int best_e = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < kPer; ++i)
+      if (s[i] > best) {                 // ascending e within a lane: the first maximum is the smallest index
+        best = s[i];
+        best_e = lane + 32 * i;
+      }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+      if (ob > best || (ob == best && oe < best_e)) {
+        best = ob;
+        best_e = oe;
+      }
+    }
+    if ((best_e & 31) == lane) {
+#pragma unroll
+      for (int i = 0; i < kPer; ++i)
+        if (lane + 32 * i == best_e) s[i] = -INFINITY;    // taken
+    }
+    const float score = 1.0f / (1.0f + expf(-best));
+    if (lane == j) {
+      chosen_w = score;
+      chosen_e = best_e;
+    }
+    total += score;
+  }
+  if (lane < top) {
+    ids[lane] = chosen_e;
+    weights[lane] = (eps < 0.f ? chosen_w : chosen_w / (total + eps)) * factor;
+  }
+}
+
 // The choice of one token by one warp: softmax over `logit(e)`, the `top` largest, renormalised.
 template <typename F>
 __device__ __forceinline__ void choose_experts(F logit, int E, int top, float eps, float factor, int lane,
-                                               int32_t* __restrict__ ids, float* __restrict__ weights) {
+                                               int32_t* __restrict__ ids, float* __restrict__ weights, int sigmoid = 0) {
+  if (sigmoid) {
+    choose_experts_sigmoid(logit, E, top, eps, factor, lane, ids, weights);
+    return;
+  }
   constexpr int kPer = kMaxExperts / 32;
   float s[kPer];
   float m = -INFINITY;
@@ -86,7 +138,7 @@ __device__ __forceinline__ void choose_experts(F logit, int E, int top, float ep
 // From given logits: one warp per token.
 __global__ void route_topk_kernel(const float* __restrict__ logits, int E, int top, float eps, float factor,
                                   const int32_t* __restrict__ req_of_token, int32_t* __restrict__ ids,
-                                  float* __restrict__ weights, int n_tokens) {
+                                  float* __restrict__ weights, int n_tokens, int sigmoid) {
   pdl_launch_dependents();
   pdl_wait();
   const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
@@ -99,7 +151,7 @@ __global__ void route_topk_kernel(const float* __restrict__ logits, int E, int t
     return;
   }
   const float* z = logits + (size_t)n * E;
-  choose_experts([&](int e) { return z[e]; }, E, top, eps, factor, lane, ids + (size_t)n * top, weights + (size_t)n * top);
+  choose_experts([&](int e) { return z[e]; }, E, top, eps, factor, lane, ids + (size_t)n * top, weights + (size_t)n * top, sigmoid);
 }
 
 // Four consecutive values of a row kept in shared memory (the address a multiple of four elements).
@@ -121,7 +173,8 @@ __device__ __forceinline__ void load4(const __nv_bfloat16* p, float& a, float& b
 template <typename T, int TOK>
 __global__ void route_kernel(const T* __restrict__ x, long x_stride, const float* __restrict__ w, int E, int K, int top,
                              float eps, float factor, const int32_t* __restrict__ req_of_token, int32_t* __restrict__ ids,
-                             float* __restrict__ weights, int n_tokens) {
+                             float* __restrict__ weights, int n_tokens, int sigmoid, const float* __restrict__ side,
+                             float* __restrict__ side_out) {
   extern __shared__ __align__(16) unsigned char route_smem[];   // [TOK][K] rows (T), then [TOK][E] logits (float)
   T* xs = reinterpret_cast<T*>(route_smem);
   float* z = reinterpret_cast<float*>(route_smem + (((size_t)TOK * K * sizeof(T) + 15) & ~(size_t)15));
@@ -146,9 +199,11 @@ __global__ void route_kernel(const T* __restrict__ x, long x_stride, const float
   }
   __syncthreads();
   // four k a lane and load where rows allow it (k = 4 lane + 128 i: one order of sums for every TOK), else one
-  const bool vec = (K & 3) == 0 && ((uintptr_t)w & 15) == 0;
-  for (int e = warp; e < E; e += warps) {
-    const float* wr = w + (size_t)e * K;
+  const bool vec = (K & 3) == 0 && ((uintptr_t)w & 15) == 0 && ((uintptr_t)side & 15) == 0;
+  // `side` [K]: one more row beside the router's, whose sigmoid goes to side_out[n] (a gate per token that reads
+  // the same rows; same order of sums as an expert's logit)
+  for (int e = warp; e < E + (side ? 1 : 0); e += warps) {
+    const float* wr = e < E ? w + (size_t)e * K : side;
     float acc[TOK];
 #pragma unroll
     for (int t = 0; t < TOK; ++t) acc[t] = 0.f;
@@ -177,7 +232,10 @@ __global__ void route_kernel(const T* __restrict__ x, long x_stride, const float
 #pragma unroll
     for (int t = 0; t < TOK; ++t) {
       const float v = warp_sum(acc[t]);
-      if (lane == 0) z[t * E + e] = v;
+      if (lane == 0) {
+        if (e < E) z[t * E + e] = v;
+        else if (t < here) side_out[n0 + t] = 1.0f / (1.0f + expf(-v));
+      }
     }
   }
   __syncthreads();
@@ -191,13 +249,14 @@ __global__ void route_kernel(const T* __restrict__ x, long x_stride, const float
       continue;
     }
     const float* zt = z + t * E;
-    choose_experts([&](int e) { return zt[e]; }, E, top, eps, factor, lane, ids + (size_t)n * top, weights + (size_t)n * top);
+    choose_experts([&](int e) { return zt[e]; }, E, top, eps, factor, lane, ids + (size_t)n * top, weights + (size_t)n * top, sigmoid);
   }
 }
 
 template <typename T, int TOK>
 int launch_route(const void* x, long x_stride, const float* w, int n_tokens, int E, int K, int top, float eps, float factor,
-                 const int32_t* req_of_token, int32_t* ids, float* weights, cudaStream_t stream) {
+                 const int32_t* req_of_token, int32_t* ids, float* weights, int sigmoid, const float* side, float* side_out,
+                 cudaStream_t stream) {
   const size_t smem = (((size_t)TOK * K * sizeof(T) + 15) & ~(size_t)15) + (size_t)TOK * E * sizeof(float);
   if (smem > 200 * 1024) return YALIS_ERR_SHAPE;
   static size_t configured = 0;
@@ -207,7 +266,7 @@ int launch_route(const void* x, long x_stride, const float* w, int n_tokens, int
     configured = smem;
   }
   return yalis_launch(route_kernel<T, TOK>, dim3((n_tokens + TOK - 1) / TOK), dim3(256), smem, stream, (const T*)x, x_stride, w, E, K,
-                      top, eps, factor, req_of_token, ids, weights, n_tokens);
+                      top, eps, factor, req_of_token, ids, weights, n_tokens, sigmoid, side, side_out);
 }
 
 // One block.  entries = n_tokens * top.  tiles: (expert, first slot) per row tile of `bm` slots, ended by n_tiles.
@@ -269,6 +328,22 @@ __global__ void gather_rows_kernel(const uint4* __restrict__ x, long x_stride16,
   if (slot >= offsets[E]) return;
   const int row = perm[slot] / top;
   for (int c = threadIdx.x; c < cols16; c += blockDim.x) out[(size_t)slot * cols16 + c] = x[(size_t)row * x_stride16 + c];
+}
+
+// xg[slot, :] = x[perm[slot] / top, :] * weights[perm[slot]] in any dtype: the rows of every expert side by side,
+// each times the weight of its (token, choice) entry (weights null: 1), float32 product, one rounding.
+template <typename T>
+__global__ void gather_scale_rows_kernel(const T* __restrict__ x, long x_stride, const int32_t* __restrict__ perm, int top,
+                                         const float* __restrict__ weights, const int32_t* __restrict__ offsets, int E,
+                                         T* __restrict__ out, int cols) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int slot = blockIdx.x;
+  if (slot >= offsets[E]) return;
+  const int entry = perm[slot], row = entry / top;
+  const float wgt = weights ? weights[entry] : 1.0f;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x)
+    out[(size_t)slot * cols + c] = from_f32<T>(to_f32<T>(x[(size_t)row * x_stride + c]) * wgt);
 }
 
 __device__ __forceinline__ float apply_act(float v, int act) {
@@ -470,7 +545,8 @@ int launch_grouped_mma(const GroupedArgs& g, int max_tiles, cudaStream_t stream)
 template <typename T>
 __global__ void expert_combine_kernel(const T* __restrict__ y, long y_stride, const int32_t* __restrict__ inv,
                                       const float* __restrict__ weights, int top, const T* __restrict__ shared,
-                                      long shared_stride, T* __restrict__ out, long out_stride, int cols) {
+                                      long shared_stride, T* __restrict__ out, long out_stride, int cols,
+                                      const float* __restrict__ shared_scale) {
   pdl_launch_dependents();
   pdl_wait();
   const int n = blockIdx.x;
@@ -478,9 +554,9 @@ __global__ void expert_combine_kernel(const T* __restrict__ y, long y_stride, co
     float acc = 0.f;
     for (int j = 0; j < top; ++j) {
       const int slot = inv[(size_t)n * top + j];
-      if (slot >= 0) acc = __fmaf_rn(weights[(size_t)n * top + j], to_f32<T>(y[(size_t)slot * y_stride + c]), acc);
+      if (slot >= 0) acc = __fmaf_rn(weights ? weights[(size_t)n * top + j] : 1.0f, to_f32<T>(y[(size_t)slot * y_stride + c]), acc);
     }
-    if (shared) acc += to_f32<T>(shared[(size_t)n * shared_stride + c]);
+    if (shared) acc = __fmaf_rn(shared_scale ? shared_scale[n] : 1.0f, to_f32<T>(shared[(size_t)n * shared_stride + c]), acc);
     out[(size_t)n * out_stride + c] = from_f32<T>(acc);
   }
 }
@@ -488,7 +564,8 @@ __global__ void expert_combine_kernel(const T* __restrict__ y, long y_stride, co
 // The same for bfloat16 rows on 16-byte boundaries: 8 columns a thread, the same order of sums per column.
 __global__ void expert_combine_bf16x8_kernel(const __nv_bfloat16* __restrict__ y, long y_stride, const int32_t* __restrict__ inv,
                                              const float* __restrict__ weights, int top, const __nv_bfloat16* __restrict__ shared,
-                                             long shared_stride, __nv_bfloat16* __restrict__ out, long out_stride, int cols) {
+                                             long shared_stride, __nv_bfloat16* __restrict__ out, long out_stride, int cols,
+                                             const float* __restrict__ shared_scale) {
   pdl_launch_dependents();
   pdl_wait();
   const int n = blockIdx.x, c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
@@ -497,7 +574,7 @@ __global__ void expert_combine_bf16x8_kernel(const __nv_bfloat16* __restrict__ y
   for (int j = 0; j < top; ++j) {
     const int slot = inv[(size_t)n * top + j];
     if (slot < 0) continue;
-    const float wj = weights[(size_t)n * top + j];
+    const float wj = weights ? weights[(size_t)n * top + j] : 1.0f;
     const uint4 raw = *reinterpret_cast<const uint4*>(y + (size_t)slot * y_stride + c);
     const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
 #pragma unroll
@@ -510,11 +587,12 @@ __global__ void expert_combine_bf16x8_kernel(const __nv_bfloat16* __restrict__ y
   if (shared) {
     const uint4 raw = *reinterpret_cast<const uint4*>(shared + (size_t)n * shared_stride + c);
     const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    const float ws = shared_scale ? shared_scale[n] : 1.0f;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const float2 v = __bfloat1622float2(h[i]);
-      acc[2 * i] += v.x;
-      acc[2 * i + 1] += v.y;
+      acc[2 * i] = __fmaf_rn(ws, v.x, acc[2 * i]);
+      acc[2 * i + 1] = __fmaf_rn(ws, v.y, acc[2 * i + 1]);
     }
   }
   uint4 res;
@@ -527,26 +605,28 @@ __global__ void expert_combine_bf16x8_kernel(const __nv_bfloat16* __restrict__ y
 }  // namespace
 
 YALIS_API int yalis_route_topk(const float* logits, int n_tokens, int E, int top, float eps, float factor, const int32_t* req_of_token,
-                               int32_t* ids, float* weights, cudaStream_t stream) {
+                               int32_t* ids, float* weights, int sigmoid, cudaStream_t stream) {
   if (n_tokens <= 0) return YALIS_OK;
   if (E <= 0 || E > kMaxExperts || top <= 0 || top > kMaxTop || top > E) return YALIS_ERR_SHAPE;
   const int warps = 4;
   return yalis_launch(route_topk_kernel, dim3((n_tokens + warps - 1) / warps), dim3(32 * warps), 0, stream, logits, E, top,
-                      eps, factor, req_of_token, ids, weights, n_tokens);
+                      eps, factor, req_of_token, ids, weights, n_tokens, sigmoid);
 }
 
 // The router and the choice in one launch.  x: [n_tokens, K] float32 or bfloat16; w: float32 [E, K].  Steps of a
 // thousand tokens and more take eight to a block where their rows fit shared memory (fewer tokens would leave SMs
 // without a block: 64 tokens in 8 blocks took 48 us, in 64 blocks 13).
 YALIS_API int yalis_route(const void* x, int x_dtype, long x_stride, const float* w, int n_tokens, int E, int K, int top, float eps, float factor,
-                          const int32_t* req_of_token, int32_t* ids, float* weights, cudaStream_t stream) {
+                          const int32_t* req_of_token, int32_t* ids, float* weights, int sigmoid, const float* side,
+                          float* side_out, cudaStream_t stream) {
   if (n_tokens <= 0) return YALIS_OK;
   if (E <= 0 || E > kMaxExperts || top <= 0 || top > kMaxTop || top > E || K <= 0) return YALIS_ERR_SHAPE;
+  if ((side == nullptr) != (side_out == nullptr)) return YALIS_ERR_SHAPE;
   const size_t elt = x_dtype == YALIS_BF16 ? 2 : 4;
   const bool many = n_tokens >= 1024 && 8 * ((size_t)K * elt + (size_t)E * 4) + 16 <= 96 * 1024;
   YALIS_DISPATCH_DTYPE(x_dtype, T,
-                       return many ? launch_route<T, 8>(x, x_stride, w, n_tokens, E, K, top, eps, factor, req_of_token, ids, weights, stream)
-                                   : launch_route<T, 1>(x, x_stride, w, n_tokens, E, K, top, eps, factor, req_of_token, ids, weights, stream));
+                       return many ? launch_route<T, 8>(x, x_stride, w, n_tokens, E, K, top, eps, factor, req_of_token, ids, weights, sigmoid, side, side_out, stream)
+                                   : launch_route<T, 1>(x, x_stride, w, n_tokens, E, K, top, eps, factor, req_of_token, ids, weights, sigmoid, side, side_out, stream));
   return YALIS_OK;
 }
 
@@ -592,9 +672,21 @@ YALIS_API int yalis_gather_rows(const void* x, long x_stride, const int32_t* per
                       (const uint4*)x, x_stride / 8, perm, top, offsets, E, (uint4*)out, K / 8);
 }
 
+// Any dtype; `weights` float32 [n_tokens * top] or null.
+YALIS_API int yalis_gather_scale_rows(const void* x, long x_stride, int dtype, const int32_t* perm, int top, const float* weights,
+                                      const int32_t* offsets, int E, void* out, int entries, int K, cudaStream_t stream) {
+  if (entries <= 0) return YALIS_OK;
+  if (top <= 0 || K <= 0) return YALIS_ERR_SHAPE;
+  YALIS_DISPATCH_DTYPE(dtype, T,
+                       return yalis_launch(gather_scale_rows_kernel<T>, dim3(entries), dim3(K < 256 ? ((K + 31) / 32) * 32 : 256), 0,
+                                           stream, (const T*)x, x_stride, perm, top, weights, offsets, E, (T*)out, K));
+  return YALIS_OK;
+}
+
+// `weights` null: every choice counts once.  `shared_scale` float32 [n_tokens] or null: a factor per token on `shared`.
 YALIS_API int yalis_expert_combine(const void* y, long y_stride, const int32_t* inv, const float* weights, int top,
                                    const void* shared, long shared_stride, void* out, long out_stride, int dtype,
-                                   int n_tokens, int cols, cudaStream_t stream) {
+                                   int n_tokens, int cols, const float* shared_scale, cudaStream_t stream) {
   if (n_tokens <= 0 || cols <= 0) return YALIS_OK;
   if (top <= 0) return YALIS_ERR_SHAPE;
   const bool aligned = dtype == YALIS_BF16 && cols % 8 == 0 && y_stride % 8 == 0 && out_stride % 8 == 0 && shared_stride % 8 == 0 &&
@@ -602,11 +694,11 @@ YALIS_API int yalis_expert_combine(const void* y, long y_stride, const int32_t* 
   if (aligned)
     return yalis_launch(expert_combine_bf16x8_kernel, dim3(n_tokens, (cols / 8 + 127) / 128), dim3(128), 0, stream,
                         (const __nv_bfloat16*)y, y_stride, inv, weights, top, (const __nv_bfloat16*)shared, shared_stride,
-                        (__nv_bfloat16*)out, out_stride, cols);
+                        (__nv_bfloat16*)out, out_stride, cols, shared_scale);
   const int col_blocks = (cols + 1023) / 1024;
   YALIS_DISPATCH_DTYPE(dtype, T,
                        return yalis_launch(expert_combine_kernel<T>, dim3(n_tokens, col_blocks), dim3(256), 0, stream, (const T*)y,
                                            y_stride, inv, weights, top, (const T*)shared, shared_stride, (T*)out,
-                                           out_stride, cols));
+                                           out_stride, cols, shared_scale));
   return YALIS_OK;
 }

@@ -17,7 +17,9 @@ struct PrepParams {
   const void* q_bias; const void* k_bias; const void* v_bias;     // model dtype, or null
   const float* q_norm; const float* k_norm; float norm_eps;       // scale over dim, or null: no norm
   const float* inv_freq; int rot_dims;                            // [rot_dims / 2], or null: no rotation
+  int rot_interleaved;                                            // pair i is (2i, 2i + 1) instead of (i, i + rot_dims / 2)
   float q_scale, k_scale;
+  float q_temp_coef; int q_temp_every;                            // every > 0: q *= 1 + coef * ln(floor((pos + 1) / every) + 1)
   void* q_out; int q_out_stride;             // [N, nq * dim]
   void* k_out; int k_out_stride;             // plain destinations (used when k_pool is null)
   void* v_out; int v_out_stride;
@@ -81,14 +83,16 @@ __global__ void qkv_prepare_kernel(const PrepParams p) {
     for (int d = lane; d < width; d += 32) xs[d] = xs[d] * r * nw[d];
   }
   __syncwarp();
-  const float factor = is_q ? p.q_scale : p.k_scale;
+  float factor = is_q ? p.q_scale : p.k_scale;
+  if (is_q && p.q_temp_every > 0) factor *= 1.0f + p.q_temp_coef * logf((float)((pos + 1) / p.q_temp_every + 1));
   const int half = p.inv_freq ? p.rot_dims >> 1 : 0;
   for (int i = lane; i < half; i += 32) {
     float sn, cs, o1, o2;
     sincosf((float)pos * p.inv_freq[i], &sn, &cs);
-    rotate_pair(xs[i], xs[i + half], cs, sn, o1, o2);
-    dst[i] = from_f32<TO>(o1 * factor);
-    dst[i + half] = from_f32<TO>(o2 * factor);
+    const int a = p.rot_interleaved ? 2 * i : i, b = p.rot_interleaved ? 2 * i + 1 : i + half;
+    rotate_pair(xs[a], xs[b], cs, sn, o1, o2);
+    dst[a] = from_f32<TO>(o1 * factor);
+    dst[b] = from_f32<TO>(o2 * factor);
   }
   for (int d = 2 * half + lane; d < width; d += 32) dst[d] = from_f32<TO>(xs[d] * factor);
 }
@@ -140,6 +144,31 @@ __global__ void activation_bf16x8_kernel(const __nv_bfloat16* __restrict__ x, in
   *reinterpret_cast<uint4*>(y + r * y_stride + c) = raw;
 }
 
+// A gated activation over rows that hold a gate part and an up part (at column offsets of one matrix):
+//   kind 0:  y = silu(g) * u
+//   kind 1:  g <- min(g, limit), u <- clamp(u, -limit, limit);  y = g * sigmoid(alpha * g) * (u + shift)
+// float32 arithmetic, one rounding.
+template <typename T>
+__global__ void gated_activation_kernel(const T* __restrict__ x, long x_stride, int gate_off, int up_off, T* __restrict__ y,
+                                        long y_stride, int rows, int cols, int kind, float limit, float alpha, float shift) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t total = (size_t)rows * cols;
+  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = e / cols, c = e - r * cols;
+    float g = to_f32<T>(x[r * x_stride + gate_off + c]), u = to_f32<T>(x[r * x_stride + up_off + c]);
+    float o;
+    if (kind == 1) {
+      g = fminf(g, limit);
+      u = fminf(fmaxf(u, -limit), limit);
+      o = g * (1.0f / (1.0f + expf(-alpha * g))) * (u + shift);
+    } else {
+      o = silu_exact(g) * u;
+    }
+    y[r * y_stride + c] = from_f32<T>(o);
+  }
+}
+
 // x[n, :] += other[n, :] + vec[:]   (either may be absent)
 __global__ void add_rows_vector_kernel(float* __restrict__ x, const float* __restrict__ other,
                                        const float* __restrict__ vec, int rows, int cols) {
@@ -159,8 +188,9 @@ __global__ void add_rows_vector_kernel(float* __restrict__ x, const float* __res
 // out_dtype: the dtype of q_out and of the plain k_out / v_out (pools always have the model dtype `dtype`).
 YALIS_API int yalis_qkv_prepare(const void* src, int dtype, int src_stride, int q_off, int k_off, int v_off,
                                 const void* q_bias, const void* k_bias, const void* v_bias, const float* q_norm,
-                                const float* k_norm, float norm_eps, const float* inv_freq, int rot_dims, float q_scale,
-                                float k_scale, void* q_out, int q_out_stride, void* k_out, int k_out_stride, void* v_out,
+                                const float* k_norm, float norm_eps, const float* inv_freq, int rot_dims,
+                                int rot_interleaved, float q_scale, float k_scale, float q_temp_coef, int q_temp_every,
+                                void* q_out, int q_out_stride, void* k_out, int k_out_stride, void* v_out,
                                 int v_out_stride, int out_dtype, void* k_pool, void* v_pool,
                                 const int32_t* block_table, int table_width, int page_size, int num_pages,
                                 const int32_t* positions, const int32_t* req_of_token, int n_tokens, int nq, int nk,
@@ -173,7 +203,8 @@ YALIS_API int yalis_qkv_prepare(const void* src, int dtype, int src_stride, int 
   PrepParams p;
   p.src = src; p.src_stride = src_stride; p.q_off = q_off; p.k_off = k_off; p.v_off = v_off;
   p.q_bias = q_bias; p.k_bias = k_bias; p.v_bias = v_bias; p.q_norm = q_norm; p.k_norm = k_norm; p.norm_eps = norm_eps;
-  p.inv_freq = inv_freq; p.rot_dims = rot_dims; p.q_scale = q_scale; p.k_scale = k_scale;
+  p.inv_freq = inv_freq; p.rot_dims = rot_dims; p.rot_interleaved = rot_interleaved; p.q_scale = q_scale; p.k_scale = k_scale;
+  p.q_temp_coef = q_temp_coef; p.q_temp_every = q_temp_every;
   p.q_out = q_out; p.q_out_stride = q_out_stride; p.k_out = k_out; p.k_out_stride = k_out_stride;
   p.v_out = v_out; p.v_out_stride = v_out_stride; p.k_pool = k_pool; p.v_pool = v_pool; p.block_table = block_table;
   p.table_width = table_width; p.page_size = page_size; p.num_pages = num_pages; p.positions = positions;
@@ -203,6 +234,20 @@ YALIS_API int yalis_activation(const void* x, int x_stride, void* y, int y_strid
   YALIS_DISPATCH_DTYPE(dtype, T,
                        return yalis_launch(activation_kernel<T>, dim3(blocks), dim3(256), 0, stream, (const T*)x, x_stride,
                                            (T*)y, y_stride, rows, cols, act));
+  return YALIS_OK;
+}
+
+YALIS_API int yalis_gated_activation(const void* x, long long x_stride, int gate_off, int up_off, void* y, long long y_stride,
+                                     int dtype, int rows, int cols, int kind, float limit, float alpha, float shift,
+                                     cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0) return YALIS_OK;
+  if (kind < 0 || kind > 1) return YALIS_ERR_SHAPE;
+  const size_t total = (size_t)rows * cols;
+  const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  YALIS_DISPATCH_DTYPE(dtype, T,
+                       return yalis_launch(gated_activation_kernel<T>, dim3(blocks), dim3(256), 0, stream, (const T*)x,
+                                           (long)x_stride, gate_off, up_off, (T*)y, (long)y_stride, rows, cols, kind, limit,
+                                           alpha, shift));
   return YALIS_OK;
 }
 

@@ -25,6 +25,7 @@ class Model:
         self.blocks: List[Block] = [build_block(layer) for layer in spec.layers]
         self.final_norm = make_part("norm", spec.final_norm)
         self.entry = make_part("entry", spec.entry) if spec.entry is not None else None
+        self.embedding_norm = make_part("norm", spec.embedding_norm) if spec.embedding_norm is not None else None
         self.embedding: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
         self.dtype: Optional[torch.dtype] = None
@@ -66,6 +67,9 @@ class Model:
         if self.entry is not None:
             for local, ps in self.entry.param_specs().items():
                 put(s.entry_names[local], ps)
+        if self.embedding_norm is not None:
+            for local, ps in self.embedding_norm.param_specs().items():
+                put(s.embedding_norm_names[local], ps)
         for tensor_name, shape in s.extra_tensors.values():
             put(tensor_name, ParamSpec(tuple(shape), keep_float32=True))
         if s.head_name is not None:
@@ -84,6 +88,8 @@ class Model:
         self.final_norm.load({local: fetch(s.final_norm_names[local]) for local in self.final_norm.param_specs()})
         if self.entry is not None:
             self.entry.load({local: fetch(s.entry_names[local]) for local in self.entry.param_specs()})
+        if self.embedding_norm is not None:
+            self.embedding_norm.load({local: fetch(s.embedding_norm_names[local]) for local in self.embedding_norm.param_specs()})
         self.head = self.embedding if s.head_name is None else fetch(s.head_name).contiguous()
         self.extra = {local: fetch(tensor_name).contiguous() for local, (tensor_name, _) in s.extra_tensors.items()}
 
@@ -105,7 +111,7 @@ class Model:
         """The keys of all parts that run in a step, or ``NOT_CAPTURABLE`` if one of them cannot be recorded."""
         keys = []
         parts = [self.blocks[i] for i in sorted({e.layer for e in self.spec.schedule})] + [self.final_norm]
-        for part in parts + ([self.entry] if self.entry is not None else []):
+        for part in parts + [p for p in (self.entry, self.embedding_norm) if p is not None]:
             key = part.capture_key(host)
             if key is NOT_CAPTURABLE:
                 return NOT_CAPTURABLE
@@ -116,8 +122,13 @@ class Model:
     def forward(self, ctx, caches: List[Optional[object]], tap: Optional[Callable] = None) -> ResidualStream:
         """``tap(i, x)``, if given, sees the float32 stream [N, hidden] (the sum of its copies, if it has several)
         after schedule entry ``i`` (every pending addition applied): for comparisons layer by layer."""
+        # a norm of the plain root-mean-square kind is applied by the kernel that gathers the rows
+        fused = self.embedding_norm.rms_parameters() if self.embedding_norm is not None else None
         x = embedding(self.embedding, ctx.token_ids, bad_flag=ctx.error_flag, scale=self.spec.embedding_scale,
-                      from_slot=ctx.token_from_slot, chosen=ctx.chosen if ctx.token_from_slot is not None else None)
+                      from_slot=ctx.token_from_slot, chosen=ctx.chosen if ctx.token_from_slot is not None else None,
+                      norm=fused)
+        if self.embedding_norm is not None and fused is None:
+            x = self.embedding_norm.normalize(x)
         if self.entry is not None:
             self.entry.forward(x, ctx, caches[len(self.spec.schedule)])
         entered = x.clone() if self._keeps_embedding else None
@@ -174,4 +185,5 @@ class Model:
         walk(self.blocks)
         walk(self.final_norm)
         walk(self.entry)
+        walk(self.embedding_norm)
         return total

@@ -40,13 +40,17 @@ def paged_attention_generic(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch
                             num_kv_heads: int, head_dim: int, scale: Optional[float] = None,
                             window: Optional[int] = None, out: Optional[torch.Tensor] = None,
                             v_head_dim: Optional[int] = None, softcap: Optional[float] = None, sink: bool = False,
-                            out_scale: float = 1.0) -> torch.Tensor:
+                            out_scale: float = 1.0, chunk: Optional[int] = None,
+                            sink_logits: Optional[torch.Tensor] = None, slopes: Optional[torch.Tensor] = None,
+                            gate: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Exact attention of every token over the cached keys of its request.
 
     ``q`` may be the fused qkv matrix (only its first heads*head_dim columns are
     read).  Token t of request r at position p sees keys j of r with
-    p - window < j <= p.  ``softcap`` c turns a score s into c * tanh(s / c); ``sink``
-    adds 1 to the softmax's denominator (a key of score 0 that has no value);
+    p - window < j <= p, and with ``chunk`` C only j >= floor(p / C) * C.  ``slopes`` (float32 [heads]) take
+    slope_h * (p - j) off the scaled score.  ``softcap`` c turns a score s into c * tanh(s / c); ``sink``
+    adds exp(z_h) to the softmax's denominator (a key of score z_h that has no value; z = ``sink_logits`` float32
+    [heads], 0 without them); ``gate`` [N, heads * v_head_dim] multiplies the result by its sigmoid;
     ``v_head_dim`` is the head size of the values when it is not the keys'.  The result,
     times ``out_scale``, is [N, heads*v_head_dim] in q's dtype (``out`` may be a
     column block of a wider matrix).
@@ -61,14 +65,27 @@ def paged_attention_generic(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch
         out = torch.empty((n, num_heads * vd), dtype=q.dtype, device=q.device)
     need(out.shape == (n, num_heads * vd) and out.dtype == q.dtype and out.stride(1) == 1, name, "bad out tensor")
     need(softcap is None or softcap > 0, name, "the soft cap must be positive")
+    _check_extras(name, q, num_heads, vd, chunk, sink, sink_logits, slopes, gate)
     if scale is None:
         scale = 1.0 / math.sqrt(head_dim)
     check(lib().yalis_paged_attention_generic(
         ptr(q), i32(q.stride(0)), ptr(out), i32(out.stride(0)), ptr(k_pool), ptr(v_pool), i32(dtype_code(q.dtype)),
         ptr(positions), ptr(req_of_token), ptr(block_table), i32(block_table.shape[1]), i32(k_pool.shape[2]),
         i32(k_pool.shape[0]), i32(n), i32(num_heads), i32(num_kv_heads), i32(head_dim), i32(vd), f32(scale),
-        i32(window or 0), f32(softcap or 0.0), i32(int(sink)), f32(out_scale), stream()), name)
+        i32(window or 0), f32(softcap or 0.0), i32(int(sink)), f32(out_scale), i32(chunk or 0), ptr(sink_logits), ptr(slopes),
+        ptr(gate), i32(gate.stride(0) if gate is not None else 0), stream()), name)
     return out
+
+
+def _check_extras(name, q, num_heads, vd, chunk, sink, sink_logits, slopes, gate):
+    need_cuda(name, sink_logits, slopes, gate)
+    need(chunk is None or chunk > 0, name, "the chunk size must be positive")
+    need(sink_logits is None or sink, name, "sink scores come with a sink")
+    for v in (sink_logits, slopes):
+        need(v is None or (v.dtype == torch.float32 and v.shape == (num_heads,) and v.is_contiguous()), name,
+             "sink scores and slopes must be float32 [heads]")
+    need(gate is None or (gate.dtype == q.dtype and gate.shape == (q.shape[0], num_heads * vd) and gate.stride(1) == 1), name,
+         "the gate must be [N, heads * v_head_dim] in q's dtype with unit inner stride")
 
 
 SM_COUNT: Optional[int] = None    # set to override what the device reports (tests pretend a small GPU)
@@ -166,12 +183,15 @@ def paged_attention_mma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Ten
                         num_heads: int, num_kv_heads: int, head_dim: int, scale: Optional[float] = None,
                         window: Optional[int] = None, n_splits: int = 1,
                         out: Optional[torch.Tensor] = None, softcap: Optional[float] = None, sink: bool = False,
-                        out_scale: float = 1.0, exact_weights: bool = False) -> torch.Tensor:
+                        out_scale: float = 1.0, exact_weights: bool = False, chunk: Optional[int] = None,
+                        sink_logits: Optional[torch.Tensor] = None, slopes: Optional[torch.Tensor] = None,
+                        gate: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Tensor-core attention (bfloat16) of the step's tokens over the cache; the same
     semantics as ``paged_attention_generic``.  ``q_start`` int32 [R+1] gives each request's
     token range; ``max_q_len`` bounds the launch grid.  ``n_splits`` > 1 divides the keys of
     a request among blocks (decode steps) and needs scratch memory for the partial results.
-    ``softcap``, ``sink`` and ``out_scale`` as in ``paged_attention_generic``; with any of them, or with
+    ``softcap``, ``sink``, ``out_scale``, ``chunk``, ``sink_logits``, ``slopes`` and ``gate`` as in
+    ``paged_attention_generic``; with any of them, or with
     ``exact_weights``, the softmax weights meet the values with 16 bits of mantissa (in two bfloat16 halves)
     instead of 8.  ``out`` may be a column block of a wider matrix if it starts on a 16-byte boundary.
     """
@@ -188,6 +208,7 @@ def paged_attention_mma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Ten
     need(out.shape == (n, num_heads * head_dim) and out.dtype == q.dtype and out.stride(1) == 1
          and out.stride(0) % 2 == 0 and out.data_ptr() % 16 == 0, name, "bad out tensor")
     need(softcap is None or softcap > 0, name, "the soft cap must be positive")
+    _check_extras(name, q, num_heads, head_dim, chunk, sink, sink_logits, slopes, gate)
     if scale is None:
         scale = 1.0 / math.sqrt(head_dim)
     scratch = tickets = None
@@ -203,7 +224,8 @@ def paged_attention_mma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Ten
         ptr(req_of_token), ptr(block_table), i32(block_table.shape[1]), i32(k_pool.shape[2]), i32(k_pool.shape[0]),
         i32(n), i32(r), i32(max_q_len), i32(num_heads), i32(num_kv_heads), i32(head_dim), f32(scale), i32(window or 0),
         i32(n_splits), ptr(scratch), ptr(tickets), f32(softcap or 0.0), i32(int(sink)), f32(out_scale),
-        i32(int(exact_weights)), stream()), name)
+        i32(int(exact_weights)), i32(chunk or 0), ptr(sink_logits), ptr(slopes), ptr(gate),
+        i32(gate.stride(0) if gate is not None else 0), stream()), name)
     return out
 
 

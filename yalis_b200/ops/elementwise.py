@@ -11,8 +11,10 @@ from ._lib import check, dtype_code, f32, i32, i64, lib, need, need_cuda, ptr, s
 
 def embedding(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor] = None,
               bad_flag: Optional[torch.Tensor] = None, scale: Optional[float] = None,
-              from_slot: Optional[torch.Tensor] = None, chosen: Optional[torch.Tensor] = None) -> torch.Tensor:
+              from_slot: Optional[torch.Tensor] = None, chosen: Optional[torch.Tensor] = None,
+              norm=None) -> torch.Tensor:
     """out[t] = float32(table[ids[t]]) (times ``scale`` if given).  ids int32 [N]; table [vocab, width].
+    ``norm`` = (weight float32 [width], eps): the rows enter normed, v / sqrt(mean(v^2) + eps) * weight.
     With ``from_slot`` (int32 [N]) and ``chosen`` (int32 vector), token t takes its id from
     ``chosen[from_slot[t]]`` where ``from_slot[t]`` is not negative."""
     name = "embedding"
@@ -28,9 +30,15 @@ def embedding(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor
     if out is None:
         out = torch.empty((n, width), dtype=torch.float32, device=table.device)
     need(out.dtype == torch.float32 and out.is_contiguous() and out.shape == (n, width), name, "out must be float32 [N, width]")
+    norm_w, norm_eps = (None, 0.0) if norm is None else norm
+    if norm_w is not None:
+        need_cuda(name, norm_w)
+        need(norm_w.dtype == torch.float32 and norm_w.shape == (width,) and norm_w.is_contiguous(), name,
+             "the norm's weight must be float32 [width]")
     check(lib().yalis_embedding(ptr(table), i32(dtype_code(table.dtype)), ptr(ids), ptr(from_slot), ptr(chosen),
                                 ptr(out), i32(n), i32(width),
-                                i32(vocab), f32(1.0 if scale is None else scale), ptr(bad_flag), stream()), name)
+                                i32(vocab), f32(1.0 if scale is None else scale), ptr(bad_flag), ptr(norm_w), f32(norm_eps),
+                                stream()), name)
     return out
 
 
@@ -78,6 +86,46 @@ def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Te
     check(lib().yalis_add_rmsnorm(ptr(x), ptr(delta), i32(d_code), i32(n_delta), i64(d_stride), ptr(weight), ptr(out),
                                   i32(dtype_code(out_dtype)), ptr(rows), i32(n_out), i32(width), f32(eps),
                                   i32(0 if rows is not None else 1), stream()), name)
+    return out
+
+
+def add_normed_rmsnorm(x: torch.Tensor, delta: torch.Tensor, *, bias: Optional[torch.Tensor] = None,
+                       delta_norm=None, weight: Optional[torch.Tensor] = None, eps: float = 0.0,
+                       out_dtype: Optional[torch.dtype] = None, rows: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """A sub-layer's result that is normed on its way into the stream, and the norm that follows, in one pass:
+
+        d = delta (the sum of split partial sums [S, N, width], in order) + bias
+        d <- d / sqrt(mean(d^2) + e_d) * w_d          with ``delta_norm`` = (w_d, e_d)
+        x <- x + d;  returns rmsnorm(x) * weight in ``out_dtype``        (nothing without ``weight``)
+
+    all float32.  With ``rows`` only those rows are computed and x is left untouched."""
+    name = "add_normed_rmsnorm"
+    d_w, d_eps = (None, 0.0) if delta_norm is None else delta_norm
+    need_cuda(name, x, delta, bias, d_w, weight, rows)
+    need(x.dtype == torch.float32 and x.dim() == 2 and x.is_contiguous(), name, "x must be contiguous float32 [N, width]")
+    n, width = x.shape
+    for v in (bias, d_w, weight):
+        need(v is None or (v.dtype == torch.float32 and v.shape == (width,) and v.is_contiguous()), name,
+             "bias and norm weights must be float32 [width]")
+    need(delta.is_contiguous(), name, "delta must be contiguous")
+    if delta.dim() == 2:
+        need(delta.shape == (n, width), name, f"delta shape {tuple(delta.shape)} != {(n, width)}")
+        n_delta, d_stride = 1, 0
+    else:
+        need(delta.dim() == 3 and delta.shape[1:] == (n, width), name, "split delta must be [S, N, width]")
+        n_delta, d_stride = delta.shape[0], n * width
+    n_out = n
+    if rows is not None:
+        need(rows.dtype == torch.int32 and rows.dim() == 1 and rows.is_contiguous(), name, "rows must be int32 [R]")
+        n_out = rows.numel()
+    out = None
+    if weight is not None:
+        need(out_dtype is not None, name, "the output needs a dtype")
+        out = torch.empty((n_out, width), dtype=out_dtype, device=x.device)
+    check(lib().yalis_add_normed_rmsnorm(ptr(x), ptr(delta), i32(dtype_code(delta.dtype)), i32(n_delta), i64(d_stride), ptr(bias),
+                                         ptr(d_w), f32(d_eps), ptr(weight), ptr(out),
+                                         i32(dtype_code(out_dtype if out is not None else torch.float32)), ptr(rows), i32(n_out),
+                                         i32(width), f32(eps), i32(0 if rows is not None else 1), stream()), name)
     return out
 
 
@@ -166,6 +214,27 @@ def gather_rows(x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
     return out
 
 
+GATED_SILU, GATED_CLAMPED = 0, 1
+
+
+def gated_activation(x: torch.Tensor, gate_off: int, up_off: int, width: int, *, kind: int = GATED_SILU, limit: float = 0.0,
+                     alpha: float = 1.0, shift: float = 0.0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """A gated activation over rows that hold a gate part g = x[:, gate_off : gate_off + width] and an up part
+    u = x[:, up_off : up_off + width]: ``GATED_SILU`` silu(g) * u; ``GATED_CLAMPED`` with g <- min(g, limit) and
+    u <- clamp(u, -limit, limit): g * sigmoid(alpha g) * (u + shift).  float32 arithmetic, one rounding."""
+    name = "gated_activation"
+    need_cuda(name, x, out)
+    need(x.dim() == 2 and x.stride(1) == 1 and max(gate_off, up_off) + width <= x.shape[1] and min(gate_off, up_off) >= 0,
+         name, "x must be [N, C] with unit inner stride and hold both parts")
+    if out is None:
+        out = torch.empty((x.shape[0], width), dtype=x.dtype, device=x.device)
+    need(out.shape == (x.shape[0], width) and out.dtype == x.dtype and out.stride(1) == 1, name, "bad out tensor")
+    check(lib().yalis_gated_activation(ptr(x), i64(x.stride(0)), i32(gate_off), i32(up_off), ptr(out), i64(out.stride(0)),
+                                       i32(dtype_code(x.dtype)), i32(x.shape[0]), i32(width), i32(kind), f32(limit), f32(alpha),
+                                       f32(shift), stream()), name)
+    return out
+
+
 ACT_GELU_ERF, ACT_GELU_TANH, ACT_SILU, ACT_RELU2, ACT_TANH = 0, 1, 2, 3, 4
 ACTIVATIONS = {"gelu": ACT_GELU_ERF, "gelu_erf": ACT_GELU_ERF, "gelu_tanh": ACT_GELU_TANH, "silu": ACT_SILU,
                "relu2": ACT_RELU2, "tanh": ACT_TANH}
@@ -205,13 +274,15 @@ def qkv_prepare(src: torch.Tensor, offsets, nq: int, nk: int, dim: int, vdim: in
                 inv_freq: Optional[torch.Tensor] = None, q_scale: float = 1.0, k_scale: float = 1.0,
                 k_pool: Optional[torch.Tensor] = None, v_pool: Optional[torch.Tensor] = None,
                 block_table: Optional[torch.Tensor] = None, store: bool = True,
-                bad_flag: Optional[torch.Tensor] = None):
+                bad_flag: Optional[torch.Tensor] = None, interleaved: bool = False, q_temperature=None):
     """Prepares the heads of a mixer from its input projection ``src`` [N, ...] (model dtype), whose query,
     key and value heads start at the columns ``offsets`` = (q, k, v):
 
         x <- x + bias;  q, k <- x / sqrt(mean(x^2) + norm_eps) * norm (where a norm is given);
         q, k <- rotation of their first 2 * len(inv_freq) sizes by the angle position * inv_freq (size i paired
-        with i + len(inv_freq)), the other sizes unchanged;  q <- q * q_scale, k <- k * k_scale.
+        with i + len(inv_freq); with ``interleaved`` size 2i with 2i + 1), the other sizes unchanged;
+        q <- q * q_scale, k <- k * k_scale;  with ``q_temperature`` = (coef, every) also
+        q <- q * (1 + coef * ln(floor((position + 1) / every) + 1)).
 
     With pools, keys [pages, nk, page_size, dim] and values [pages, nk, page_size, vdim] are written to the pages
     of ``block_table`` (not at all when ``store`` is False) and the queries [N, nq * dim] are returned.  Without
@@ -235,6 +306,7 @@ def qkv_prepare(src: torch.Tensor, offsets, nq: int, nk: int, dim: int, vdim: in
         need(inv_freq.dtype == torch.float32 and inv_freq.dim() == 1 and inv_freq.is_contiguous()
              and 2 * inv_freq.numel() <= dim, name, "inv_freq must be float32 [rot_dims / 2], rot_dims <= dim")
         rot_dims = 2 * inv_freq.numel()
+    need(q_temperature is None or int(q_temperature[1]) > 0, name, "the query temperature's period must be positive")
     paged = k_pool is not None
     q_out = torch.empty((n, nq * dim), dtype=out_dtype, device=src.device)
     k_out = v_out = None
@@ -257,7 +329,9 @@ def qkv_prepare(src: torch.Tensor, offsets, nq: int, nk: int, dim: int, vdim: in
     check(lib().yalis_qkv_prepare(
         ptr(src), i32(dtype_code(src.dtype)), i32(src.stride(0)), i32(q_off), i32(k_off), i32(v_off),
         ptr(biases[0]), ptr(biases[1]), ptr(biases[2]), ptr(q_norm), ptr(k_norm), f32(norm_eps), ptr(inv_freq),
-        i32(rot_dims), f32(q_scale), f32(k_scale), ptr(q_out), i32(q_out.stride(0)), ptr(k_out),
+        i32(rot_dims), i32(int(interleaved)), f32(q_scale), f32(k_scale),
+        f32(q_temperature[0] if q_temperature is not None else 0.0), i32(q_temperature[1] if q_temperature is not None else 0),
+        ptr(q_out), i32(q_out.stride(0)), ptr(k_out),
         i32(k_out.stride(0) if k_out is not None else 0), ptr(v_out), i32(v_out.stride(0) if v_out is not None else 0),
         i32(dtype_code(out_dtype)), ptr(k_pool if store else None), ptr(v_pool if store else None), ptr(block_table),
         i32(table_width), i32(page_size), i32(num_pages), ptr(positions), ptr(req_of_token), i32(n), i32(nq), i32(nk),

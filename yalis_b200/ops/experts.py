@@ -16,10 +16,11 @@ ACT_NONE, ACT_RELU2 = 0, 1
 
 
 def route_topk(logits: torch.Tensor, top: int, eps: Optional[float] = 1e-20, req_of_token: Optional[torch.Tensor] = None,
-               factor: float = 1.0):
+               factor: float = 1.0, score: str = "softmax"):
     """(ids int32 [N, top], weights float32 [N, top]): the ``top`` largest of softmax(logits) per row (ties to the
     smaller index) and those scores divided by their sum + eps (``eps`` None: the scores as they are), times
-    ``factor``.  Rows of no request get ids -1."""
+    ``factor``.  ``score`` = ``sigmoid``: the scores are sigmoid(logits), each on its own.  Rows of no request get
+    ids -1."""
     name = "route_topk"
     need_cuda(name, logits, req_of_token)
     need(logits.dtype == torch.float32 and logits.dim() == 2 and logits.is_contiguous(), name, "logits must be contiguous float32 [N, E]")
@@ -28,16 +29,26 @@ def route_topk(logits: torch.Tensor, top: int, eps: Optional[float] = 1e-20, req
     ids = torch.empty((n, top), dtype=torch.int32, device=logits.device)
     weights = torch.empty((n, top), dtype=torch.float32, device=logits.device)
     check(lib().yalis_route_topk(ptr(logits), i32(n), i32(e), i32(top), f32(-1.0 if eps is None else eps), f32(factor), ptr(req_of_token), ptr(ids), ptr(weights),
-                                 stream()), name)
+                                 i32(_score_code(name, score)), stream()), name)
     return ids, weights
 
 
+def _score_code(name: str, score: str) -> int:
+    need(score in ("softmax", "sigmoid"), name, f"unknown score {score!r} (softmax or sigmoid)")
+    return int(score == "sigmoid")
+
+
 def route(x: torch.Tensor, router: torch.Tensor, top: int, eps: Optional[float] = 1e-20, req_of_token: Optional[torch.Tensor] = None,
-          factor: float = 1.0):
+          factor: float = 1.0, score: str = "softmax", side: Optional[torch.Tensor] = None):
     """``route_topk`` of the logits ``x router^T`` in one launch: ``x`` [N, K] (float32 or bfloat16, unit inner stride),
-    ``router`` float32 [E, K].  The logits are float32 sums in a fixed order per (token, expert)."""
+    ``router`` float32 [E, K].  The logits are float32 sums in a fixed order per (token, expert).  With ``side``
+    (float32 [K]) a third result is returned: float32 [N], sigmoid(x . side), a gate per token from the same rows."""
     name = "route"
-    need_cuda(name, x, router, req_of_token)
+    need_cuda(name, x, router, req_of_token, side)
+    side_out = None
+    if side is not None:
+        need(side.dtype == torch.float32 and side.shape == (x.shape[1],) and side.is_contiguous(), name, "side must be float32 [K]")
+        side_out = torch.zeros(x.shape[0], dtype=torch.float32, device=x.device)
     need(x.dim() == 2 and x.stride(1) == 1 and router.dtype == torch.float32 and router.dim() == 2 and router.is_contiguous()
          and router.shape[1] == x.shape[1], name, "x [N, K], router contiguous float32 [E, K]")
     n, e = x.shape[0], router.shape[0]
@@ -45,8 +56,9 @@ def route(x: torch.Tensor, router: torch.Tensor, top: int, eps: Optional[float] 
     ids = torch.empty((n, top), dtype=torch.int32, device=x.device)
     weights = torch.empty((n, top), dtype=torch.float32, device=x.device)
     check(lib().yalis_route(ptr(x), i32(dtype_code(x.dtype)), i64(x.stride(0)), ptr(router), i32(n), i32(e), i32(x.shape[1]), i32(top),
-                            f32(-1.0 if eps is None else eps), f32(factor), ptr(req_of_token), ptr(ids), ptr(weights), stream()), name)
-    return ids, weights
+                            f32(-1.0 if eps is None else eps), f32(factor), ptr(req_of_token), ptr(ids), ptr(weights),
+                            i32(_score_code(name, score)), ptr(side), ptr(side_out), stream()), name)
+    return (ids, weights) if side is None else (ids, weights, side_out)
 
 
 @dataclass
@@ -136,6 +148,21 @@ def gather_rows(x: torch.Tensor, plan: ExpertPlan, top: int) -> torch.Tensor:
     return out
 
 
+def gather_scale_rows(x: torch.Tensor, plan: ExpertPlan, top: int, weights: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """[entries, K]: row ``perm[slot] // top`` of ``x`` for every slot in use, times ``weights[perm[slot]]`` (float32
+    [N, top]; None: as it is): what an expert reads when a choice's weight multiplies its input.  Any dtype."""
+    name = "gather_scale_rows"
+    need_cuda(name, x, weights)
+    need(x.dim() == 2 and x.stride(1) == 1, name, "x must be [N, K] with unit inner stride")
+    need(weights is None or (weights.dtype == torch.float32 and weights.is_contiguous() and weights.numel() == plan.entries), name,
+         "weights must be contiguous float32 [N, top]")
+    out = torch.empty((plan.entries, x.shape[1]), dtype=x.dtype, device=x.device)
+    check(lib().yalis_gather_scale_rows(ptr(x), i64(x.stride(0)), i32(dtype_code(x.dtype)), ptr(plan.perm), i32(top), ptr(weights),
+                                        ptr(plan.offsets), i32(plan.offsets.numel() - 1), ptr(out), i32(plan.entries),
+                                        i32(x.shape[1]), stream()), name)
+    return out
+
+
 def grouped_gemm_wstream(a: torch.Tensor, w: torch.Tensor, plan: ExpertPlan, *, act: int = ACT_NONE) -> torch.Tensor:
     """C[s, :] = act(A[s, :] . w[expert(s)]^T) on tcgen05 tensor cores with TMA-streamed operands: ``a`` [entries, K]
     holds one row per slot (see ``gather_rows``), ``w`` [E, n_out, K]; the plan's row tile is one of ``WSTREAM_TILES``."""
@@ -153,13 +180,21 @@ def grouped_gemm_wstream(a: torch.Tensor, w: torch.Tensor, plan: ExpertPlan, *, 
     return out
 
 
-def expert_combine(y: torch.Tensor, plan: ExpertPlan, weights: torch.Tensor, shared: Optional[torch.Tensor] = None,
-                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out[n, :] = sum_j weights[n, j] * y[inv[n, j], :] (+ shared[n, :]), float32 sums in the order of j."""
+def expert_combine(y: torch.Tensor, plan: ExpertPlan, weights: Optional[torch.Tensor], shared: Optional[torch.Tensor] = None,
+                   out: Optional[torch.Tensor] = None, top: Optional[int] = None,
+                   shared_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[n, :] = sum_j weights[n, j] * y[inv[n, j], :] (+ shared_scale[n] * shared[n, :]), float32 sums in the order of
+    j.  ``weights`` None (then ``top`` says how many choices a token has): every choice counts once."""
     name = "expert_combine"
-    need_cuda(name, y, weights, shared, out)
-    n, top = weights.shape
-    need(weights.dtype == torch.float32 and weights.is_contiguous() and n * top == plan.entries, name, "weights: float32 [N, top]")
+    need_cuda(name, y, weights, shared, out, shared_scale)
+    if weights is None:
+        need(top is not None and top > 0 and plan.entries % top == 0, name, "without weights, top must be given")
+        n = plan.entries // top
+    else:
+        n, top = weights.shape
+        need(weights.dtype == torch.float32 and weights.is_contiguous() and n * top == plan.entries, name, "weights: float32 [N, top]")
+    need(shared_scale is None or (shared is not None and shared_scale.dtype == torch.float32 and shared_scale.shape == (n,)
+                                  and shared_scale.is_contiguous()), name, "shared_scale: float32 [N], with shared")
     need(y.dim() == 2 and y.shape[0] == plan.entries and y.stride(1) == 1, name, "y must be [N * top, C]")
     cols = y.shape[1]
     if shared is not None:
@@ -169,5 +204,5 @@ def expert_combine(y: torch.Tensor, plan: ExpertPlan, weights: torch.Tensor, sha
     need(out.shape == (n, cols) and out.dtype == y.dtype and out.stride(1) == 1, name, "bad out tensor")
     check(lib().yalis_expert_combine(ptr(y), i64(y.stride(0)), ptr(plan.inv), ptr(weights), i32(top), ptr(shared),
                                      i64(shared.stride(0) if shared is not None else 0), ptr(out), i64(out.stride(0)),
-                                     i32(dtype_code(y.dtype)), i32(n), i32(cols), stream()), name)
+                                     i32(dtype_code(y.dtype)), i32(n), i32(cols), ptr(shared_scale), stream()), name)
     return out

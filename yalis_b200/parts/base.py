@@ -151,13 +151,26 @@ class PendingWrite:
                 "out_weights": self.out_weights}
 
 
+@dataclass
+class NormedSum:
+    """A sub-layer's result that is not added as it is: ``bias`` (float32 [hidden]) is added to it, and with ``norm`` =
+    (weight float32 [hidden], eps) the sum is normed, d / sqrt(mean(d^2) + eps) * weight, before it joins the stream
+    (an arrangement with a norm behind each sub-layer).  ``y`` is [N, hidden] in the model dtype or float32 partial
+    sums [P, N, hidden].  All of it is float32 arithmetic inside the pass that adds it."""
+
+    y: torch.Tensor
+    bias: Optional[torch.Tensor] = None
+    norm: Optional[Tuple[torch.Tensor, float]] = None
+
+
 class ResidualStream:
     """The float32 residual stream [N, hidden] with one pending delta.
 
     A sub-layer's output is not added at once: it is parked in ``pending`` and
     the next norm adds it while it reads the stream (one pass instead of two).
     ``pending`` is [N, hidden] in the model dtype, or float32 split partial sums
-    [S, N, hidden] that are added in order.
+    [S, N, hidden] that are added in order, or a ``NormedSum`` (such a tensor with a bias, a norm of its own
+    or both).
 
     A model may keep the stream in several copies: ``x`` is then [N, copies, hidden], what is parked is a
     ``PendingWrite``, and the norms and arrangements that know such streams read and write all copies in one pass.
@@ -168,7 +181,7 @@ class ResidualStream:
     def __init__(self, x: torch.Tensor, dtype: torch.dtype, source: Optional[torch.Tensor] = None):
         self.x = x
         self.dtype = dtype
-        self.pending = None       # a tensor (see above) or a PendingWrite
+        self.pending = None       # a tensor (see above), a NormedSum or a PendingWrite
         self.source = source
 
     def take_source(self, stores: bool = True) -> Optional[torch.Tensor]:
@@ -191,6 +204,8 @@ class ResidualStream:
         self.flush()
         if self.x.dim() == 3 and not isinstance(delta, PendingWrite):
             raise ValueError("a stream kept in several copies takes a PendingWrite, not a plain sum")
+        if isinstance(delta, NormedSum) and delta.bias is None and delta.norm is None:
+            delta = delta.y
         self.pending = delta
 
     def flush(self) -> None:
@@ -199,6 +214,9 @@ class ResidualStream:
         if isinstance(self.pending, PendingWrite):
             from yalis_b200.ops.streams import stream_step
             stream_step(self.x, read=False, source=self.take_source(), **self.pending.arguments())
+        elif isinstance(self.pending, NormedSum):
+            from yalis_b200.ops.elementwise import add_normed_rmsnorm
+            add_normed_rmsnorm(self.x, self.pending.y, bias=self.pending.bias, delta_norm=self.pending.norm)
         else:
             from yalis_b200.ops.elementwise import residual_add
             residual_add(self.x, self.pending)
@@ -264,6 +282,11 @@ class Norm(Part):
         """The norm of a plain tensor [N, width] in its own dtype (for arrangements that norm a sub-layer's
         output rather than the stream)."""
         raise NotImplementedError
+
+    def rms_parameters(self) -> Optional[Tuple[torch.Tensor, float]]:
+        """(weight float32 [width], eps) if the norm is x / sqrt(mean(x^2) + eps) * weight and nothing else, so that a
+        kernel which produces or consumes the rows can apply it itself; None (the default) otherwise."""
+        return None
 
 
 NOT_ROTARY = object()     # answer of PositionEncoding.rotary_frequencies for encodings a mixer's kernel cannot apply itself

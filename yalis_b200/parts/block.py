@@ -7,30 +7,54 @@ from typing import Optional
 import torch
 
 from yalis_b200.ops.linear import linear, linear_partial
-from .base import Block, Projected, ResidualStream, register_part, stack_rows
+from .base import Block, NormedSum, Projected, ResidualStream, register_part, stack_rows
 
 
 class PreNormResidualBlock(Block):
     """x += mixer(norm_1(x)); x += feed_forward(norm_2(x))
     (the non-parallel branch of yalis/external/model.py:414-438).
     Each addition is parked in the stream and performed by the next norm.  A layer may leave out the position part
-    (a mixer that sees to positions itself) and the feed-forward with its norm."""
+    (a mixer that sees to positions itself) and the feed-forward with its norm.
 
-    slots = {"position": "position", "norm_1": "norm", "mixer": "mixer", "norm_2": "norm",
-             "feed_forward": "feed_forward"}
-    optional = ("position", "norm_2", "feed_forward")
+    With ``norm_1_post`` / ``norm_2_post`` a sub-layer's result is normed before it is added:
+    x += norm_1_post(mixer(norm_1(x))); x += norm_2_post(feed_forward(norm_2(x))).  A norm of the plain
+    root-mean-square kind rides along with the result (``NormedSum``) and is applied, in float32, by the pass
+    that adds it; any other kind norms the result on its own first."""
+
+    slots = {"position": "position", "norm_1": "norm", "mixer": "mixer", "norm_1_post": "norm", "norm_2": "norm",
+             "feed_forward": "feed_forward", "norm_2_post": "norm"}
+    optional = ("position", "norm_2", "feed_forward", "norm_1_post", "norm_2_post")
 
     def __init__(self, spec, parts):
         super().__init__(spec, parts)
         if ("norm_2" in self.parts) != ("feed_forward" in self.parts):
             raise ValueError("a pre-norm block has a feed-forward and its norm, or neither")
+        if "norm_2_post" in self.parts and "feed_forward" not in self.parts:
+            raise ValueError("a norm behind the feed-forward needs a feed-forward")
+
+    @staticmethod
+    def _normed(result, norm):
+        """A sub-layer's result with the norm that follows it."""
+        if norm is None:
+            return result
+        if not isinstance(result, NormedSum):
+            result = NormedSum(result)
+        if result.norm is not None:
+            raise ValueError("the result already carries a norm")
+        params = norm.rms_parameters()
+        if params is not None:
+            return NormedSum(result.y, result.bias, params)
+        y = result.y if result.y.dim() == 2 else result.y.sum(dim=0)
+        if result.bias is not None:
+            y = y.float() + result.bias
+        return norm.normalize(y.to(result.y.dtype if result.y.dim() == 2 else torch.float32).contiguous())
 
     def forward(self, stream: ResidualStream, ctx, cache) -> None:
         h = self.norm_1.forward(stream)
-        stream.add(self.mixer.forward(h, ctx, cache))
+        stream.add(self._normed(self.mixer.forward(h, ctx, cache), self.parts.get("norm_1_post")))
         if "feed_forward" in self.parts:
             h = self.norm_2.forward(stream)
-            stream.add(self.feed_forward.forward(h, ctx))
+            stream.add(self._normed(self.feed_forward.forward(h, ctx), self.parts.get("norm_2_post")))
 
 
 class ParallelResidualBlock(Block):

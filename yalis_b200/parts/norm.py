@@ -8,8 +8,8 @@ from typing import Dict, Optional
 import torch
 
 from yalis_b200.config.spec import PartSpec
-from yalis_b200.ops.elementwise import add_rmsnorm
-from .base import Norm, ParamSpec, PendingWrite, ResidualStream, register_part
+from yalis_b200.ops.elementwise import add_normed_rmsnorm, add_rmsnorm
+from .base import Norm, NormedSum, ParamSpec, PendingWrite, ResidualStream, register_part
 
 
 class RMSNorm(Norm):
@@ -36,7 +36,12 @@ class RMSNorm(Norm):
         stream.materialize()
         if isinstance(stream.pending, PendingWrite):
             stream.flush()
-        y = add_rmsnorm(stream.x, stream.pending, self.weight, self.eps, stream.dtype, rows=rows)
+        if isinstance(stream.pending, NormedSum):      # a result with a bias or a norm of its own: the same single pass
+            pend = stream.pending
+            y = add_normed_rmsnorm(stream.x, pend.y, bias=pend.bias, delta_norm=pend.norm, weight=self.weight, eps=self.eps,
+                                   out_dtype=stream.dtype, rows=rows)
+        else:
+            y = add_rmsnorm(stream.x, stream.pending, self.weight, self.eps, stream.dtype, rows=rows)
         if rows is None:
             stream.pending = None   # the kernel has written x + delta back
         return y
@@ -45,6 +50,9 @@ class RMSNorm(Norm):
         # the same kernel over a zero stream with y as its pending delta: float32 math, one rounding
         zero = torch.zeros(y.shape, dtype=torch.float32, device=y.device)
         return add_rmsnorm(zero, y.contiguous(), self.weight, self.eps, y.dtype)
+
+    def rms_parameters(self):
+        return self.weight, self.eps
 
     def capture_key(self, host):
         return None
@@ -76,6 +84,8 @@ class DynamicTanh(Norm):
                 in_weights: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``in_weights`` [copies]: the weights of the copies in the sum that is normed (None: the plain sum)."""
         from yalis_b200.ops.streams import stream_step
+        if isinstance(stream.pending, NormedSum):
+            stream.flush()
         pending = stream.pending
         write = pending.arguments() if isinstance(pending, PendingWrite) else ({"y": pending} if pending is not None else {})
         h = stream_step(stream.x, norm=self.triple(), in_weights=in_weights, rows=rows, out_dtype=stream.dtype,

@@ -30,12 +30,14 @@ from .base import Mixer, ParamSpec, PositionEncoding, Projected, SlotState, Slot
 
 
 def position_part(params) -> Optional[PositionEncoding]:
-    """The position part a mixer builds for itself from its ``rotary`` parameter ({"dims", "theta"}; None: none)."""
+    """The position part a mixer builds for itself from its ``rotary`` parameter ({"dims", "theta"} and optionally
+    "layout"; None: none)."""
     rot = params.get("rotary")
     if rot is None:
         return None
     return make_part("position", PartSpec("rotary", {"head_dim": int(rot["dims"]), "theta": float(rot["theta"]),
-                                                     "scaling": None, "exact_powers": True}))
+                                                     "scaling": None, "exact_powers": True,
+                                                     "layout": rot.get("layout", "half")}))
 
 
 class _ProjectedMixer(Mixer, Projected):
