@@ -8,6 +8,7 @@ Llama-3-8B shape (random weights, bfloat16, page size 16), batch 8, 1,024-token 
     python bench.py --workload mixers [--sizes 1b,3b]           # Tirezen beside the Llama shape of equal size
     python bench.py --workload mixers --family vepivik          # the same for Vepivik
     python bench.py --workload mixers --family pametar          # Pametar beside the Vepivik shape of equal size
+    python bench.py --workload mixers --family sazavik          # Sazavik beside the Vepivik shape of equal size
 
 A "step" is one decode step of the whole batch.  ``value`` is decoded tokens per second
 with the K steps timed on the device (CUDA events) and the chosen tokens fed back on
@@ -40,7 +41,9 @@ choose, of a windowed layer no more keys than its window).  ``value`` is the fam
 batch 8 of the first size.  ``--family vepivik`` runs the Vepivik presets (windowed attention, attention over a
 cached latent, routed experts) beside the same Llama shapes.  ``--family pametar`` runs the Pametar presets (a stream in
 four copies, generalized delta rule, latent attention with a sink, routed experts) beside the Vepivik presets of the same
-width, expert count and latent sizes.
+width, expert count and latent sizes.  ``--family sazavik`` runs the Sazavik presets (chunked and windowed attention with
+sinks, gates and a distance bias, norms on both sides of every sub-layer, dense and routed feed-forwards) beside the
+Vepivik presets of the same width, head and expert counts.
 """
 
 from __future__ import annotations
@@ -286,7 +289,7 @@ def run_mixers(args) -> int:
 
     peaks, peak_source = load_peaks()
     family = args.family
-    beside = {"1b": "vepivik-1b", "3b": "vepivik-3b"} if family == "pametar" else {"1b": "Llama-3.2-1B", "3b": "Llama-3.2-3B"}
+    beside = {"1b": "vepivik-1b", "3b": "vepivik-3b"} if family in ("pametar", "sazavik") else {"1b": "Llama-3.2-1B", "3b": "Llama-3.2-3B"}
     pairs = {size: (f"{family}-{size}", other) for size, other in beside.items()}
     steps = args.steps or 64
     warm = max(3, args.warmup or 8)
@@ -354,7 +357,7 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decode-8b", choices=["decode-8b", "mixed-1b", "serve-3b", "mixers"])
     ap.add_argument("--sizes", default="1b,3b", help="for --workload mixers: which pairs of models to run")
-    ap.add_argument("--family", default="tirezen", choices=["tirezen", "vepivik", "pametar"],
+    ap.add_argument("--family", default="tirezen", choices=["tirezen", "vepivik", "pametar", "sazavik"],
                     help="for --workload mixers: the family whose presets run beside the Llama shapes")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--page-size", type=int, default=None, help="tokens per cache page (default: 16 as the benchmark "

@@ -191,10 +191,22 @@ def route(h, t, prefix, top):
     return ids, ws
 
 
-def moe_ff(h, t, prefix, mlp):
+def route_margins(h, t, prefix, top):
+    """Per token, how far the last chosen logit lies above the first one left out (inf when every expert is chosen):
+    where this is small, reduced precision may choose otherwise."""
+    z = h @ t[prefix + "router"].T
+    if top >= z.shape[1]:
+        return torch.full((z.shape[0],), float("inf"), dtype=z.dtype)
+    srt = torch.sort(z, dim=1, descending=True).values
+    return srt[:, top - 1] - srt[:, top]
+
+
+def moe_ff(h, t, prefix, mlp, margins=None):
     """Every token's input, times the chosen expert's score, goes through that expert; the shared expert is
     weighted by one sigmoid per token."""
     ids, ws = route(h, t, prefix, mlp["router"]["top"])
+    if margins is not None:
+        margins.append(route_margins(h, t, prefix, mlp["router"]["top"]))
     out = torch.zeros_like(h)
     for n in range(h.shape[0]):
         for e, w in zip(ids[n], ws[n]):
@@ -206,8 +218,9 @@ def moe_ff(h, t, prefix, mlp):
 
 # ---- the model ---------------------------------------------------------------------------------------------------
 
-def forward(config, tensors, tokens, dtype=torch.float64, taps=None):
-    """Logits [T, vocab] of one sequence.  ``taps``: a list that receives the stream after every layer."""
+def forward(config, tensors, tokens, dtype=torch.float64, taps=None, margins=None):
+    """Logits [T, vocab] of one sequence.  ``taps``: a list that receives the stream after every layer.  ``margins``: a
+    list that receives, per routed layer, every token's ``route_margins``."""
     t = {k: (v.to(dtype) if v.dtype.is_floating_point else v) for k, v in tensors.items()}
     eps = config["norm"]["eps"]
     positions = torch.arange(len(tokens))
@@ -222,7 +235,7 @@ def forward(config, tensors, tokens, dtype=torch.float64, taps=None):
         mlp = layer.get("mlp")
         if mlp is not None:
             h = stream_norm(x, t[p + "norm2"], eps)
-            y = dense_ff(h, t, p + "mlp.", mlp["limit"]) if mlp["kind"] == "dense" else moe_ff(h, t, p + "mlp.", mlp)
+            y = dense_ff(h, t, p + "mlp.", mlp["limit"]) if mlp["kind"] == "dense" else moe_ff(h, t, p + "mlp.", mlp, margins)
             x = x + stream_norm(y, t[p + "norm2b"], eps)
         if taps is not None:
             taps.append(x.clone())

@@ -283,15 +283,16 @@ def test_token_rows_are_normed_as_they_enter():
 
 # ---- feed-forwards ---------------------------------------------------------------------------------------------------
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_the_clamped_gated_activation(dtype):
+@pytest.mark.parametrize("dtype, at", [(torch.float32, 5), (torch.bfloat16, 5), (torch.bfloat16, 8)])
+def test_the_clamped_gated_activation(dtype, at):
+    """``at`` = 8 puts both parts on 16-byte boundaries (the kernel that takes eight values a thread), 5 does not."""
     from yalis_b200.ops.elementwise import GATED_CLAMPED, gated_activation
     g = torch.Generator().manual_seed(2)
     n, inner, limit = 11, 40, 1.25
-    z = (torch.randn(n, 5 + 2 * inner, generator=g) * 2).to(dtype)           # values on both sides of the limit
-    out = gated_activation(z.to(DEV), 5, 5 + inner, inner, kind=GATED_CLAMPED, limit=limit, alpha=1.702, shift=1.0)
-    gate = torch.clamp(z[:, 5:5 + inner].double(), max=limit)
-    up = torch.clamp(z[:, 5 + inner:].double(), min=-limit, max=limit)
+    z = (torch.randn(n, at + 2 * inner, generator=g) * 2).to(dtype)           # values on both sides of the limit
+    out = gated_activation(z.to(DEV), at, at + inner, inner, kind=GATED_CLAMPED, limit=limit, alpha=1.702, shift=1.0)
+    gate = torch.clamp(z[:, at:at + inner].double(), max=limit)
+    up = torch.clamp(z[:, at + inner:].double(), min=-limit, max=limit)
     want = gate * torch.sigmoid(1.702 * gate) * (up + 1)
     assert float(gate.max()) == limit and float(up.min()) == -limit and float(gate.min()) < -limit          # the gate has no floor
     tol = 1e-5 if dtype == torch.float32 else 2e-2
@@ -382,11 +383,34 @@ def requests_for(which):
     return {f"r{i}": torch.randint(0, cfg["vocab"], (n,), generator=g).tolist() for i, n in enumerate(LENGTHS[which])}
 
 
+CLOSE_CALL = 0.05        # a chosen router logit this near to one left out may go the other way in bfloat16
+_close = {}
+
+
 def oracle(which):
     if which not in _oracle:
         cfg, w = plain.read_folder(sazavik_dir(which))
-        _oracle[which] = {rid: plain.forward(cfg, w, t).numpy() for rid, t in requests_for(which).items()}
+        _oracle[which], _close[which] = {}, {}
+        for rid, t in requests_for(which).items():
+            margins = []
+            _oracle[which][rid] = plain.forward(cfg, w, t, margins=margins).numpy()
+            _close[which][rid] = after_close_calls(cfg, margins, len(t))
     return _oracle[which]
+
+
+def after_close_calls(cfg, margins, n):
+    """Per position: whether a router's close call lies at it or within reach before it.  Under bfloat16 such a token
+    may run another expert than the float64 model; its keys and values in the layers above then differ, and with them
+    every later position that still sees it.  These positions are left out of the bfloat16 comparison; all others
+    must agree."""
+    reach = max(layer["mixer"]["mask"]["size"] for layer in cfg["layers"])
+    close = np.zeros(n, dtype=bool)
+    if margins:
+        close = (torch.stack(margins).min(dim=0).values < CLOSE_CALL).numpy()
+    out = np.zeros(n, dtype=bool)
+    for p in np.where(close)[0]:
+        out[p:min(n, p + 2 * reach)] = True          # twice: a disturbed position disturbs those that see it once more
+    return out
 
 
 def replay(which, dtype, steps, max_tokens, graphs=False):
@@ -403,7 +427,10 @@ def replay(which, dtype, steps, max_tokens, graphs=False):
     return out, rep
 
 
-def compare(got, want, tol, what, outliers=0.0):
+def compare(got, want, tol, what, skip=None, outliers=0.15):
+    """Every position agrees.  With ``skip`` (bfloat16; per request, the positions after a router's close call, see
+    ``after_close_calls``): every other position agrees, and of all positions at most ``outliers``, skipped or not,
+    differ (a model with many experts has close calls everywhere, and little would be left to compare otherwise)."""
     assert set(got) == set(want), what
     total = bad = 0
     for rid in want:
@@ -412,7 +439,9 @@ def compare(got, want, tol, what, outliers=0.0):
         err = np.abs(got[rid] - want[rid]).max(axis=1) / scale
         total += len(err)
         bad += int((err > tol).sum())
-        if err.max() > tol and not outliers:
+        if skip is not None:
+            err = np.where(skip[rid], 0.0, err)
+        if err.max() > tol:
             raise AssertionError(f"{what}: request {rid} differs by {err.max():.3e} (tolerance {tol}); first wrong "
                                  f"position {int(np.argmax(err > tol))} of {len(err)}")
     assert bad <= outliers * total, f"{what}: {bad} of {total} positions differ by more than {tol}"
@@ -424,14 +453,13 @@ def test_requests_cut_four_ways_agree_with_the_plain_model(which, dtype):
     reqs, want = requests_for(which), oracle(which)
     vocab = plain.read_folder(sazavik_dir(which))[0]["vocab"]
     results = {}
-    # bfloat16: a token whose two best router scores are nearly equal may run another expert than the float64 model
-    outliers = 0.0 if dtype == "float32" else 0.08
+    skip = None if dtype == "float32" else _close[which]
     for name, steps in (("whole", traces.whole(reqs)), ("tail", traces.tail_decoded(reqs, tail=12)),
                         ("portions", traces.portions(reqs, seed=3)), ("mixed", traces.mixed(reqs, seed=5, tail=6))):
         steps = traces.number(steps)
         out, rep = replay(which, dtype, steps, traces.peak_tokens(steps, max(64, PAGE[which])))
         got = traces.collect(steps, out, vocab)
-        compare(got, want, TOL[dtype], f"{which} {dtype} {name}", outliers=outliers)
+        compare(got, want, TOL[dtype], f"{which} {dtype} {name}", skip=skip)
         results[name] = got
     # how a request was cut, what ran beside it and which pages and slots it had leave (nearly) no trace
     for name in ("tail", "portions", "mixed"):
@@ -441,7 +469,7 @@ def test_requests_cut_four_ways_agree_with_the_plain_model(which, dtype):
             if dtype == "float32":
                 assert diff.max() < 2e-5, (name, rid)
             else:
-                assert np.mean(diff > 6e-2) <= outliers, (name, rid)
+                assert np.where(skip[rid], 0.0, diff).max() < 6e-2, (name, rid)
 
 
 @pytest.mark.parametrize("which", ["A", "C"])
@@ -487,7 +515,8 @@ def test_long_decoding_keeps_to_the_plain_model(which, dtype):
     cfg, w = plain.read_folder(d)
     g = torch.Generator().manual_seed(9)
     tokens = torch.randint(0, cfg["vocab"], (302,), generator=g).tolist()
-    want = plain.forward(cfg, w, tokens).numpy()
+    margins = []
+    want = plain.forward(cfg, w, tokens, margins=margins).numpy()
     eng = Engine(d, dtype=dtype, page_size=8, num_pages=14, max_slots=2, max_context=384)
     eng.add_request("x")
     rows = [eng.run([StepEntry("x", tokens[:2], [0, 1])]).logits.cpu().numpy()]
@@ -499,7 +528,8 @@ def test_long_decoding_keeps_to_the_plain_model(which, dtype):
     if dtype == "float32":
         assert err.max() < 2e-4
     else:
-        assert np.mean(err > 6e-2) < 0.08
+        skip = after_close_calls(cfg, margins, len(tokens))
+        assert np.where(skip, 0.0, err).max() < 6e-2 and np.mean(err > 6e-2) < 0.15
 
 
 def test_a_slot_and_its_pages_used_again_start_clean():

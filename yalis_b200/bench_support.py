@@ -31,7 +31,11 @@ def model_numbers(engine: Engine) -> Dict[str, object]:
         for leaf in cache_leaves(req):
             if isinstance(leaf, PagedKV):
                 mixer = m.blocks[entry.layer].parts.get("mixer")
-                paged.append((leaf.num_kv_heads * (leaf.head_dim + leaf.value_dim) * elt, getattr(mixer, "window", leaf.window)))
+                # how many keys the query at a position sees: the mixer's own rule (a window, a chunk) where it has one
+                seen = getattr(mixer, "keys_seen", None)
+                window = getattr(mixer, "window", leaf.window)
+                paged.append((leaf.num_kv_heads * (leaf.head_dim + leaf.value_dim) * elt,
+                              seen if seen is not None else (lambda pos, w=window: pos + 1 if w is None else min(pos + 1, w))))
         if entry.cache_of is not None:
             continue               # reads what another entry keeps: counted above as read, not below as kept
         for leaf in cache_leaves(req):
@@ -64,7 +68,7 @@ def model_numbers(engine: Engine) -> Dict[str, object]:
 
     def kv_bytes_at(context: float) -> float:
         """Cache bytes one single-token query reads with ``context`` tokens cached: per layer run no more than its window."""
-        return sum(per_token * (context if window is None else min(context, window)) for per_token, window in paged)
+        return sum(per_token * seen(int(context)) for per_token, seen in paged)
 
     return {"weight_bytes_per_step": weight_bytes, "kv_bytes_per_token": kv_per_token, "flops_prefill": flops_prefill,
             "matrix_flops_per_token": matrix_flops, "state_bytes_per_request": state_per_request,

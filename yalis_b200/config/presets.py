@@ -356,10 +356,11 @@ PRESETS["sazavik-tiny-D"] = _sazavik(48, 64, [
     _sz_layer(_sz_mixer("attention_2", 2, 2, 8, 24, 4096, 0.3, rot=(4, 9.0)), _moe(2, 2, 20, 12)),
     _sz_layer(_sz_mixer("attention", 2, 2, 16, 8, 4096, 0.25, rot=(16, 7.0)), _sz_dense(36, 50.0)),
     _sz_layer(_sz_mixer("attention_3", 4, 4, 8, 8, 4096, 0.3, q_temp=(0.5, 4096)), _moe(2, 2, 20, 12))], softcap=40.0)
-# Sizes that resemble a real model's layers (random weights, for the benchmark): the widths, head and expert counts of
-# the Vepivik benchmark models, so that the two designs stand beside each other at equal size.
-PRESETS["sazavik-1b"] = _sazavik_stack(2048, 32000, 4, 16, 8, 128, 2048, 1024, 4096, 16, 2, 1408, 2048)
-PRESETS["sazavik-3b"] = _sazavik_stack(3072, 32000, 6, 24, 8, 128, 2048, 1024, 6144, 32, 4, 1024, 3072)
+# Sizes that resemble a real model's layers (random weights, for the benchmark): the widths, head counts and windows of
+# the Vepivik benchmark models and, with half the layers dense, twice their experts, so that the two designs stand
+# beside each other at equal size (2.7 and 8.7 billion weights).
+PRESETS["sazavik-1b"] = _sazavik_stack(2048, 32000, 4, 16, 8, 128, 2048, 1024, 4096, 32, 2, 1408, 2048)
+PRESETS["sazavik-3b"] = _sazavik_stack(3072, 32000, 6, 24, 8, 128, 2048, 1024, 6144, 64, 4, 1024, 3072)
 
 
 def preset(name: str) -> Dict[str, Any]:

@@ -365,6 +365,123 @@ __global__ void __launch_bounds__(1024) add_normed_rmsnorm_kernel(float* __restr
   for (int c = threadIdx.x; c < width; c += blockDim.x) yr[c] = from_f32<T>((row_s[c] * inv) * w[c]);
 }
 
+// The same for rows whose width is a multiple of four and whose pointers are 16-byte aligned: a thread keeps NV
+// groups of four columns in registers from the first load to the last store (no shared-memory row), and the three
+// weight vectors are fetched before the wait for the preceding kernel.  Same order of sums per element as above
+// except inside the two means, which are fixed-order block reductions in both.
+template <typename T, typename TD, int NV>
+__global__ void __launch_bounds__(NV == 1 ? 1024 : 256) add_normed_rmsnorm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta,
+                                                                      int n_delta, size_t delta_stride,
+                                                                      const float* __restrict__ bias,
+                                                                      const float* __restrict__ d_w, float d_eps,
+                                                                      const float* __restrict__ w, T* __restrict__ y,
+                                                                      const int32_t* __restrict__ rows, int width, float eps,
+                                                                      int write_back) {
+  __shared__ float scratch[32];
+  pdl_launch_dependents();
+  const int n4 = width >> 2;
+  const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  float4 bv[NV], dwv[NV], wv[NV];
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    const int c = threadIdx.x + v * blockDim.x;
+    const bool in = c < n4;
+    bv[v] = (in && bias) ? load4_f32(bias + 4 * c) : zero4;
+    dwv[v] = (in && d_w) ? load4_f32(d_w + 4 * c) : zero4;
+    wv[v] = (in && w) ? load4_f32(w + 4 * c) : zero4;
+  }
+  pdl_wait();
+  const int i = blockIdx.x;
+  const int r = rows ? rows[i] : i;
+  if (r < 0) return;  // padded row
+  float* xr = x + (size_t)r * width;
+  const TD* dr = delta + (size_t)r * width;
+  float4 d[NV], h[NV];
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    const int c = threadIdx.x + v * blockDim.x;
+    h[v] = c < n4 ? load4_f32(xr + 4 * c) : zero4;
+    d[v] = zero4;
+  }
+  constexpr int SB = 8 / NV;       // partial sums loaded per batch; they are added in index order
+  for (int s0 = 0; s0 < n_delta; s0 += SB) {
+    float4 t[SB][NV];
+#pragma unroll
+    for (int j = 0; j < SB; ++j) {
+#pragma unroll
+      for (int v = 0; v < NV; ++v) {
+        const int c = threadIdx.x + v * blockDim.x;
+        t[j][v] = (s0 + j < n_delta && c < n4) ? load4_f32(dr + (size_t)(s0 + j) * delta_stride + 4 * c) : zero4;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < SB; ++j) {
+#pragma unroll
+      for (int v = 0; v < NV; ++v) {
+        d[v].x += t[j][v].x; d[v].y += t[j][v].y; d[v].z += t[j][v].z; d[v].w += t[j][v].w;
+      }
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    d[v].x += bv[v].x; d[v].y += bv[v].y; d[v].z += bv[v].z; d[v].w += bv[v].w;
+    ss += (d[v].x * d[v].x + d[v].y * d[v].y) + (d[v].z * d[v].z + d[v].w * d[v].w);
+  }
+  if (d_w) {
+    const float d_inv = rsqrtf(block_sum(ss, scratch) / (float)width + d_eps);
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      d[v].x = (d[v].x * d_inv) * dwv[v].x; d[v].y = (d[v].y * d_inv) * dwv[v].y;
+      d[v].z = (d[v].z * d_inv) * dwv[v].z; d[v].w = (d[v].w * d_inv) * dwv[v].w;
+    }
+  }
+  ss = 0.f;
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    const int c = threadIdx.x + v * blockDim.x;
+    h[v].x += d[v].x; h[v].y += d[v].y; h[v].z += d[v].z; h[v].w += d[v].w;
+    if (write_back && c < n4) store4(xr + 4 * c, h[v]);
+    ss += (h[v].x * h[v].x + h[v].y * h[v].y) + (h[v].z * h[v].z + h[v].w * h[v].w);
+  }
+  if (w == nullptr) return;
+  const float inv = rsqrtf(block_sum(ss, scratch) / (float)width + eps);
+  T* yr = y + (size_t)i * width;
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    const int c = threadIdx.x + v * blockDim.x;
+    if (c < n4)
+      store4(yr + 4 * c, make_float4((h[v].x * inv) * wv[v].x, (h[v].y * inv) * wv[v].y, (h[v].z * inv) * wv[v].z,
+                                     (h[v].w * inv) * wv[v].w));
+  }
+}
+
+template <typename T, typename TD>
+int launch_add_normed_rmsnorm(float* x, const void* delta, int n_delta, size_t delta_stride, const float* bias, const float* d_w,
+                              float d_eps, const float* w, void* y, const int32_t* rows, int n_out_rows, int width, float eps,
+                              int write_back, cudaStream_t stream) {
+  const uintptr_t ptrs = (uintptr_t)x | (uintptr_t)delta | (uintptr_t)bias | (uintptr_t)d_w | (uintptr_t)w | (uintptr_t)y;
+  if (width % 4 == 0 && width <= 16384 && (ptrs & 15) == 0 && delta_stride % 4 == 0) {
+    const int n4 = width / 4;
+    // few rows: a thread per group of four where a block can hold them; otherwise 256 threads a row with up to four
+    // groups each (more rows in flight per SM, registers to spare); wider rows take the shared-memory form below
+    const int cap = (n_out_rows < 256 && n4 <= 1024) ? 1024 : 256;
+    const int vthreads = n4 >= cap ? cap : (n4 + 31) / 32 * 32;
+    const int nv = (n4 + vthreads - 1) / vthreads;
+#define YALIS_NNORM_VEC(V)                                                                                           \
+  return yalis_launch(add_normed_rmsnorm_vec_kernel<T, TD, V>, dim3(n_out_rows), dim3(vthreads), 0, stream, x,       \
+                      (const TD*)delta, n_delta, delta_stride, bias, d_w, d_eps, w, (T*)y, rows, width, eps, write_back)
+    if (nv == 1) YALIS_NNORM_VEC(1);
+    else if (nv == 2) YALIS_NNORM_VEC(2);
+    else if (nv <= 4) YALIS_NNORM_VEC(4);
+#undef YALIS_NNORM_VEC
+  }
+  if (width > 48 * 1024 / 4) return YALIS_ERR_SHAPE;
+  const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+  return yalis_launch(add_normed_rmsnorm_kernel<T, TD>, dim3(n_out_rows), dim3(threads), (size_t)width * sizeof(float), stream, x,
+                      (const TD*)delta, n_delta, delta_stride, bias, d_w, d_eps, w, (T*)y, rows, width, eps, write_back);
+}
+
 // delta: [n_delta][rows_total][width] in delta_dtype; bias, d_w, w float32 [width] or null; y in out_dtype (unused
 // without w).
 YALIS_API int yalis_add_normed_rmsnorm(float* x, const void* delta, int delta_dtype, int n_delta, long long delta_stride,
@@ -372,19 +489,15 @@ YALIS_API int yalis_add_normed_rmsnorm(float* x, const void* delta, int delta_dt
                                        int out_dtype, const int32_t* rows, int n_out_rows, int width, float eps,
                                        int write_back, cudaStream_t stream) {
   if (n_out_rows <= 0) return YALIS_OK;
-  if (delta == nullptr || n_delta <= 0 || width <= 0 || width > 48 * 1024 / 4) return YALIS_ERR_SHAPE;
-  const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
-  const size_t smem = (size_t)width * sizeof(float);
+  if (delta == nullptr || n_delta <= 0 || width <= 0) return YALIS_ERR_SHAPE;
   YALIS_DISPATCH_DTYPE(
       out_dtype, T,
       if (delta_dtype == YALIS_F32) {
-        return yalis_launch(add_normed_rmsnorm_kernel<T, float>, dim3(n_out_rows), dim3(threads), smem, stream, x,
-                            (const float*)delta, n_delta, (size_t)delta_stride, bias, d_w, d_eps, w, (T*)y, rows, width, eps,
-                            write_back);
+        return launch_add_normed_rmsnorm<T, float>(x, delta, n_delta, (size_t)delta_stride, bias, d_w, d_eps, w, y, rows,
+                                                   n_out_rows, width, eps, write_back, stream);
       } else if (delta_dtype == YALIS_BF16) {
-        return yalis_launch(add_normed_rmsnorm_kernel<T, __nv_bfloat16>, dim3(n_out_rows), dim3(threads), smem, stream, x,
-                            (const __nv_bfloat16*)delta, n_delta, (size_t)delta_stride, bias, d_w, d_eps, w, (T*)y, rows, width,
-                            eps, write_back);
+        return launch_add_normed_rmsnorm<T, __nv_bfloat16>(x, delta, n_delta, (size_t)delta_stride, bias, d_w, d_eps, w, y, rows,
+                                                           n_out_rows, width, eps, write_back, stream);
       } else { return YALIS_ERR_DTYPE; });
   return YALIS_OK;
 }
