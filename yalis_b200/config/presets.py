@@ -358,7 +358,7 @@ PRESETS["sazavik-tiny-D"] = _sazavik(48, 64, [
     _sz_layer(_sz_mixer("attention_3", 4, 4, 8, 8, 4096, 0.3, q_temp=(0.5, 4096)), _moe(2, 2, 20, 12))], softcap=40.0)
 # Sizes that resemble a real model's layers (random weights, for the benchmark): the widths, head counts and windows of
 # the Vepivik benchmark models and, with half the layers dense, twice their experts, so that the two designs stand
-# beside each other at equal size (2.7 and 8.7 billion weights).
+# beside each other at about equal size (2.9 and 9.2 billion weights beside 2.6 and 8.5).
 PRESETS["sazavik-1b"] = _sazavik_stack(2048, 32000, 4, 16, 8, 128, 2048, 1024, 4096, 32, 2, 1408, 2048)
 PRESETS["sazavik-3b"] = _sazavik_stack(3072, 32000, 6, 24, 8, 128, 2048, 1024, 6144, 64, 4, 1024, 3072)
 

@@ -59,17 +59,6 @@ __global__ void embedding_kernel(const T* __restrict__ table, const int32_t* __r
   }
 }
 
-YALIS_API int yalis_embedding(const void* table, int dtype, const int32_t* ids, const int32_t* from_slot,
-                              const int32_t* chosen, float* out, int n_tokens, int width, int vocab, float scale,
-                              int32_t* bad_id, const float* norm_w, float norm_eps, cudaStream_t stream) {
-  if (n_tokens <= 0) return YALIS_OK;
-  if ((from_slot == nullptr) != (chosen == nullptr)) return YALIS_ERR_SHAPE;
-  YALIS_DISPATCH_DTYPE(dtype, T,
-                       return yalis_launch(embedding_kernel<T>, dim3(n_tokens), dim3(256), 0, stream, (const T*)table,
-                                           ids, from_slot, chosen, out, width, vocab, scale, bad_id, norm_w, norm_eps));
-  return YALIS_OK;
-}
-
 // --------------------------------------------------------------------------
 // Soft cap of float32 logits in place: v <- cap * tanh(v / cap).
 // --------------------------------------------------------------------------
@@ -194,6 +183,64 @@ __device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
   u.x = *reinterpret_cast<unsigned*>(&a);
   u.y = *reinterpret_cast<unsigned*>(&b);
   *reinterpret_cast<uint2*>(p) = u;
+}
+
+// The normed embedding for rows whose width is a multiple of four and at most 4096: a thread keeps up to four groups
+// of four values in registers between the sum of squares and the store, so the table row is read once.
+template <typename T>
+__global__ void embedding_norm_vec_kernel(const T* __restrict__ table, const int32_t* __restrict__ ids,
+                                          const int32_t* __restrict__ from_slot, const int32_t* __restrict__ chosen,
+                                          float* __restrict__ out, int width, int vocab, float scale, int32_t* bad_id,
+                                          const float* __restrict__ norm_w, float norm_eps) {
+  __shared__ float scratch[32];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x, n4 = width >> 2;
+  int id = ids[t];
+  if (from_slot != nullptr) {
+    const int s = from_slot[t];
+    if (s >= 0) id = chosen[s];
+  }
+  float* o = out + (size_t)t * width;
+  const bool bad = id < 0 || id >= vocab;
+  if (bad && threadIdx.x == 0 && bad_id) atomicOr(bad_id, YALIS_FLAG_BAD_ID);
+  const T* row = table + (size_t)(bad ? 0 : id) * width;
+  float4 v[4];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int c = threadIdx.x + j * blockDim.x;
+    v[j] = (c < n4 && !bad) ? load4_f32(row + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    v[j].x *= scale; v[j].y *= scale; v[j].z *= scale; v[j].w *= scale;
+    ss = __fmaf_rn(v[j].x, v[j].x, ss); ss = __fmaf_rn(v[j].y, v[j].y, ss);
+    ss = __fmaf_rn(v[j].z, v[j].z, ss); ss = __fmaf_rn(v[j].w, v[j].w, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = bad ? 0.f : 1.0f / sqrtf(ss / (float)width + norm_eps);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int c = threadIdx.x + j * blockDim.x;
+    if (c < n4) {
+      const float4 w = load4_f32(norm_w + 4 * c);
+      store4(o + 4 * c, make_float4((v[j].x * inv) * w.x, (v[j].y * inv) * w.y, (v[j].z * inv) * w.z, (v[j].w * inv) * w.w));
+    }
+  }
+}
+
+YALIS_API int yalis_embedding(const void* table, int dtype, const int32_t* ids, const int32_t* from_slot,
+                              const int32_t* chosen, float* out, int n_tokens, int width, int vocab, float scale,
+                              int32_t* bad_id, const float* norm_w, float norm_eps, cudaStream_t stream) {
+  if (n_tokens <= 0) return YALIS_OK;
+  if ((from_slot == nullptr) != (chosen == nullptr)) return YALIS_ERR_SHAPE;
+  if (norm_w != nullptr && width % 4 == 0 && width <= 4096 && !(((uintptr_t)table | (uintptr_t)out | (uintptr_t)norm_w) & 15)) {
+    YALIS_DISPATCH_DTYPE(dtype, T,
+                         return yalis_launch(embedding_norm_vec_kernel<T>, dim3(n_tokens), dim3(256), 0, stream, (const T*)table,
+                                             ids, from_slot, chosen, out, width, vocab, scale, bad_id, norm_w, norm_eps));
+  }
+  YALIS_DISPATCH_DTYPE(dtype, T,
+                       return yalis_launch(embedding_kernel<T>, dim3(n_tokens), dim3(256), 0, stream, (const T*)table,
+                                           ids, from_slot, chosen, out, width, vocab, scale, bad_id, norm_w, norm_eps));
+  return YALIS_OK;
 }
 
 // The same norm for rows whose width is a multiple of four and whose pointers are 16-byte aligned:
@@ -370,7 +417,7 @@ __global__ void __launch_bounds__(1024) add_normed_rmsnorm_kernel(float* __restr
 // weight vectors are fetched before the wait for the preceding kernel.  Same order of sums per element as above
 // except inside the two means, which are fixed-order block reductions in both.
 template <typename T, typename TD, int NV>
-__global__ void __launch_bounds__(NV == 1 ? 1024 : 256) add_normed_rmsnorm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta,
+__global__ void __launch_bounds__(NV == 1 ? 1024 : 256, NV == 2 ? 3 : 1) add_normed_rmsnorm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta,
                                                                       int n_delta, size_t delta_stride,
                                                                       const float* __restrict__ bias,
                                                                       const float* __restrict__ d_w, float d_eps,
