@@ -576,3 +576,82 @@ def test_the_replay_program_runs_a_sazavik_folder(tmp_path):
     vocab = plain.read_folder(sazavik_dir("B"))[0]["vocab"]
     outputs = {s["step"]: np.fromfile(out_dir / f"{s['step']}.f32", dtype="<f4") for s in steps}
     compare(traces.collect(steps, outputs, vocab), {k: oracle("B")[k] for k in reqs}, TOL["float32"], "program")
+
+
+# ---- configurations drawn at random: other orders of layers, sizes, masks and constants -------------------------------
+
+def random_config(seed):
+    """A Sazavik configuration drawn from ``seed``: three to six layers of any type in any order, head sizes with and
+    without a tensor-core kernel, key and value sizes apart or equal, masks from one position to longer than any
+    request, readers of an earlier layer's keys for every type, every kind of feed-forward."""
+    import random
+    rng = random.Random(seed)
+    width = rng.choice([40, 64, 72, 100])
+    layers, owners = [], {}          # owners: type -> [(index, mixer)] of layers with keys of their own
+    for i in range(rng.randint(3, 6)):
+        kind = rng.choice(["attention", "attention_2", "attention_3"])
+        reuse = rng.random() < 0.35 and owners.get(kind)
+        if reuse:
+            j, src = rng.choice(owners[kind])
+            kv_heads, dim, vdim = src["kv_heads"], src["dim"], src["vdim"]
+        else:
+            kv_heads, dim = rng.choice([1, 2, 3]), rng.choice([8, 12, 16, 24, 32, 40, 48, 64])
+            vdim = rng.choice([dim, dim, rng.choice([8, 20, 32])])
+        mixer = {"heads": kv_heads * rng.choice([1, 2, 4]), "kv_heads": kv_heads, "dim": dim, "vdim": vdim,
+                 "mask": {"size": rng.choice([1, 2, 5, 16, 17, 31, 64, 1000])}, "scale": round(rng.uniform(0.5, 1.5) * dim ** -0.5, 4)}
+        if kind == "attention_3":
+            mixer["q_temp"] = {"coef": round(rng.uniform(0.1, 1.0), 3), "every": rng.choice([1, 3, 16, 500])}
+        elif reuse:
+            mixer["rot"] = dict(src["rot"])
+        else:
+            mixer["rot"] = {"dims": rng.choice([d for d in (2, 4, 8, dim // 2 * 2, dim) if d <= dim and d % 2 == 0]),
+                            "base": rng.choice([10.0, 777.0, 10000.0])}
+        if reuse:
+            mixer["kv_from"] = j
+        else:
+            owners.setdefault(kind, []).append((i, mixer))
+        pick = rng.random()
+        if pick < 0.15:
+            mlp = None
+        elif pick < 0.5:
+            mlp = {"kind": "dense", "ff": rng.choice([24, 56, 90]), "limit": rng.choice([0.5, 2.0, 30.0])}
+        else:
+            experts = rng.choice([2, 3, 8, 12])
+            mlp = {"kind": "moe", "expert": {"ff": rng.choice([8, 20, 48])},
+                   "router": {"experts": experts, "top": rng.randint(1, min(experts, 4))}}
+            if rng.random() < 0.6:
+                mlp["shared"] = {"ff": rng.choice([8, 36])}
+        layers.append({"type": kind, "mixer": mixer, "mlp": mlp})
+    cfg = {"architecture": "Sazavik", "width": width, "vocab": rng.choice([33, 64, 150]), "norm": {"eps": rng.choice([1e-5, 1e-6, 1e-3])},
+           "layers": layers}
+    if rng.random() < 0.7:
+        cfg["logit_softcap"] = rng.choice([5.0, 30.0])
+    return cfg
+
+
+@pytest.mark.parametrize("seed", [11, 12, 13, 14, 15, 16, 17, 18])
+def test_configurations_drawn_at_random(seed, tmp_path):
+    from sazavik_models import write_model
+    from yalis_b200.engine.replay import Replayer
+    raw = random_config(seed)
+    d = write_model(raw, str(tmp_path / "m"), seed)
+    cfg, w = plain.read_folder(d)
+    g = torch.Generator().manual_seed(seed)
+    reqs = {f"r{i}": torch.randint(0, cfg["vocab"], (n,), generator=g).tolist() for i, n in enumerate([1, 37, 80, 9, 52])}
+    want = {rid: plain.forward(cfg, w, t).numpy() for rid, t in reqs.items()}
+    results = {}
+    for name, steps in (("whole", traces.whole(reqs)), ("mixed", traces.mixed(reqs, seed=seed, tail=5)),
+                        ("portions", traces.portions(reqs, seed=seed))):
+        steps = traces.number(steps)
+        rep = Replayer(d, "float32", traces.peak_tokens(steps), page_size=16)
+        out = {s["step"]: r for s in steps if (r := rep.run_step(s)) is not None}
+        rep.engine.manager.check()
+        results[name] = traces.collect(steps, out, cfg["vocab"])
+        compare(results[name], want, TOL["float32"], f"seed {seed} {name}")
+    # bfloat16 runs the other kernels over the same steps: no fault, and most positions near the float64 model
+    steps = traces.number(traces.mixed(reqs, seed=seed, tail=5))
+    rep = Replayer(d, "bfloat16", traces.peak_tokens(steps), page_size=16)
+    out = {s["step"]: r for s in steps if (r := rep.run_step(s)) is not None}
+    got = traces.collect(steps, out, cfg["vocab"])
+    errs = np.concatenate([np.abs(got[rid] - want[rid]).max(axis=1) / np.abs(want[rid]).max() for rid in want])
+    assert np.isfinite(errs).all() and np.mean(errs > 8e-2) < 0.25, f"seed {seed}: {np.mean(errs > 8e-2):.2f} of the positions differ"
